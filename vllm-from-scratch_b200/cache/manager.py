@@ -5,7 +5,8 @@ A *group* is a set of layer executions with the same need: all keys, or a window
 of them.  Each group has a pool of pages of its own (``cache/pool.py``) and its
 own block table per request.  Pages come back when a request ends, when it is
 preempted, and, in a windowed group, as soon as every position they hold lies
-before the window of all positions still to be computed.  The reference has one
+before the window of all positions still to be computed (but for the pages of
+the first positions, where a group keeps those readable whatever the window).  The reference has one
 group for Qwen3 and frees nothing mid-request (minivllm/core/
 single_type_kv_cache_manager.py:180-201); the allocation rule (atomic: all or
 nothing), the prefix hashing and the hit cap follow minivllm/core/
@@ -33,7 +34,7 @@ class _Held:
     slot: int
     # Per group: logical page index -> physical page (RELEASED once given back).
     pages: list[list[int]]
-    released: list[int]                 # per group: leading pages already given back
+    released: list[int]                 # per group: pages before this one (and behind the kept first ones) are given back
     hashes: list[bytes] = field(default_factory=list)   # chained hash of each full page of tokens
     published: int = 0                  # full pages already offered to the prefix cache
 
@@ -41,13 +42,19 @@ class _Held:
 class CacheManager:
     def __init__(self, group_windows: list[int | None], page_size: int, num_pages: int,
                  max_requests: int, enable_prefix_caching: bool = False,
-                 has_state: bool = False) -> None:
+                 has_state: bool = False, group_keep_first: list[int] | None = None) -> None:
         if page_size <= 0:
             raise ValueError(f"page_size must be positive, got {page_size}")
         if max_requests <= 0:
             raise ValueError(f"max_requests must be positive, got {max_requests}")
         self.page_size = page_size
         self.group_windows = list(group_windows)
+        # Per group: how many leading pages a windowed group never gives back while the request
+        # lives, because the first positions of a sequence stay readable whatever the window.
+        keep = list(group_keep_first) if group_keep_first is not None else [0] * len(self.group_windows)
+        if len(keep) != len(self.group_windows) or any(k < 0 for k in keep):
+            raise ValueError(f"group_keep_first {keep} does not fit the {len(self.group_windows)} groups")
+        self.group_kept_pages = [-(-k // page_size) for k in keep]
         self.pools = [PagePool(num_pages) for _ in self.group_windows]
         self.max_requests = max_requests
         # A published prefix can stand for a request's past only where every group
@@ -66,7 +73,7 @@ class CacheManager:
         if not self._free_slots:
             raise CacheError(f"all {self.max_requests} request slots are taken")
         slot = self._free_slots.pop()
-        self._held[request_id] = _Held(slot, [[] for _ in self.pools], [0] * len(self.pools))
+        self._held[request_id] = _Held(slot, [[] for _ in self.pools], list(self.group_kept_pages))
         self._fresh_slots.add(slot)
         return slot
 
@@ -185,7 +192,7 @@ class CacheManager:
             live = [page for page in held.pages[group] if page != RELEASED]
             pool.give_back(list(reversed(live)))       # tail first: evicted before its prefix
             held.pages[group] = []
-            held.released[group] = 0
+            held.released[group] = self.group_kept_pages[group]
         held.published = 0
         held.hashes = []
         self._fresh_slots.add(held.slot)

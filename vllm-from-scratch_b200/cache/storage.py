@@ -63,7 +63,8 @@ class CacheStorage:
         for index, (pages, _) in enumerate(split):
             if pages is not None:
                 value_dim = pages.value_dim if pages.value_dim not in (None, pages.head_dim) else None
-                key = (pages.num_kv_heads, pages.head_dim, pages.window, value_dim)
+                key = (pages.num_kv_heads, pages.head_dim, pages.window, value_dim,
+                       pages.keep_first if pages.window is not None else 0)
                 group = group_of_key.setdefault(key, len(group_of_key))
                 members.setdefault(group, []).append(index)
         page_views: dict[int, tuple[int, torch.Tensor, torch.Tensor]] = {}
@@ -140,6 +141,11 @@ class CacheStorage:
     @property
     def group_windows(self) -> list[int | None]:
         return [group.need.window for group in self.groups]
+
+    @property
+    def group_keep_first(self) -> list[int]:
+        """Per group: the first positions of a sequence that stay readable whatever the window."""
+        return [group.need.keep_first for group in self.groups]
 
     @property
     def has_state(self) -> bool:

@@ -32,7 +32,8 @@ EXTRA_FLAGS: dict[str, list[str]] = {
     "gemm_bf16": ["-lcuda"],
 }
 LIBRARIES = ("norm", "rope_cache", "attention_generic", "gemm_f32", "attention_bf16", "gemm_bf16",
-             "sampling", "decode_attention_static", "norm_ext", "attention_bias", "recurrence", "grouped")
+             "sampling", "decode_attention_static", "norm_ext", "attention_bias", "recurrence", "grouped", "streams",
+             "diff_attention")
 
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()

@@ -1,8 +1,8 @@
 // Products in groups, and what a routed feed-forward needs around them.
 //
-//   route_experts      router logits in float32, sigmoid scores, a correction added for the choice
+//   route_experts      router logits in float32, sigmoid scores (or a softmax over all of them), a correction added for the choice
 //                      only, the best groups of neighbouring experts, the `top` best experts of
-//                      those groups; weights are the plain scores of the chosen
+//                      those groups; weights are the plain scores of the chosen, or those divided by their sum
 //   expert_lists       from the chosen experts of every token: how many rows each expert has, where
 //                      its rows begin, and each (token, choice) pair's row
 //   grouped_gemm       C_g = A_g W_g^T for every group g, W_g [N, K] row-major.  The rows of a group
@@ -55,11 +55,11 @@ template <typename T>
 __global__ void route_experts_kernel(const T* __restrict__ x, const float* __restrict__ router,
                                      const float* __restrict__ correction, int* __restrict__ ids,
                                      float* __restrict__ weights, int K, int E, int top, int group_count,
-                                     int group_keep, int group_top) {
+                                     int group_keep, int group_top, int softmax_scores, int renormalise) {
     overlap_trigger();
     overlap_wait();
     extern __shared__ float route_smem[];
-    float* score = route_smem;              // [E] sigmoid of the logit
+    float* score = route_smem;              // [E] sigmoid of the logit, or the softmax over all logits
     float* choice = score + E;              // [E] score + correction, -inf outside the kept groups
     float* marks = choice + E;              // [group_count]
     const int token = blockIdx.x;
@@ -85,12 +85,24 @@ __global__ void route_experts_kernel(const T* __restrict__ x, const float* __res
             for (int k = lane; k < K; k += 32) sum = fmaf(w[k], to_float(row[k]), sum);
         }
         sum = warp_sum(sum);
-        if (lane == 0) {
-            const float s = sigmoid_fn(sum);
-            score[e] = s;
-            choice[e] = correction ? s + correction[e] : s;
-        }
+        if (lane == 0) score[e] = softmax_scores ? sum : sigmoid_fn(sum);
     }
+    __syncthreads();
+    if (softmax_scores) {
+        // one warp: the largest logit, the sum of the exponentials (every lane's share and the order of the
+        // lanes depend on E alone), then every score
+        if (warp == 0) {
+            float top_logit = -INFINITY;
+            for (int e = lane; e < E; e += 32) top_logit = fmaxf(top_logit, score[e]);
+            top_logit = warp_max(top_logit);
+            float total = 0.0f;
+            for (int e = lane; e < E; e += 32) total += expf(score[e] - top_logit);
+            total = warp_sum(total);
+            for (int e = lane; e < E; e += 32) score[e] = expf(score[e] - top_logit) / total;
+        }
+        __syncthreads();
+    }
+    for (int e = threadIdx.x; e < E; e += blockDim.x) choice[e] = correction ? score[e] + correction[e] : score[e];
     __syncthreads();
     if (group_count > 1 && group_keep < group_count) {
         const int per = E / group_count;
@@ -124,7 +136,7 @@ __global__ void route_experts_kernel(const T* __restrict__ x, const float* __res
         __syncthreads();
     }
     if (warp != 0) return;
-    float pv = INFINITY;
+    float pv = INFINITY, chosen_sum = 0.0f;
     int pi = -1;
     for (int j = 0; j < top; ++j) {
         float bv = -INFINITY;
@@ -145,9 +157,13 @@ __global__ void route_experts_kernel(const T* __restrict__ x, const float* __res
             ids[(size_t)token * top + j] = bi;
             weights[(size_t)token * top + j] = score[bi];
         }
+        chosen_sum += score[bi];            // every lane holds the same choice: one sum in the order of the choices
         pv = bv;
         pi = bi;
     }
+    if (renormalise && lane == 0)
+        for (int j = 0; j < top; ++j)
+            weights[(size_t)token * top + j] = score[ids[(size_t)token * top + j]] / (chosen_sum + 1e-20f);
 }
 
 // One block.  offsets [E + 1]; sorted_pair [pairs]: the pairs (token * top + choice) expert by expert;
@@ -176,6 +192,9 @@ __global__ void expert_lists_kernel(const int* __restrict__ ids, int pairs, int 
         offsets[E] = running;
     }
     __syncthreads();
+    // Pairs whose expert has no list (a number outside [0, E)) leave rows past the last list unused: they
+    // name the first pair, so that whoever gathers rows by this list reads a row that exists.
+    for (int p = offsets[E] + threadIdx.x; p < pairs; p += blockDim.x) sorted_pair[p] = 0;
     // Pairs of one expert keep no particular order among themselves; a row's result does not depend
     // on where in its expert's list it stands.
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) {
@@ -189,21 +208,29 @@ __global__ void expert_lists_kernel(const int* __restrict__ ids, int pairs, int 
 
 template <typename T>
 __global__ void combine_experts_kernel(const T* __restrict__ rows, const int* __restrict__ position,
-                                       const float* __restrict__ weights, T* __restrict__ out, int width, int top) {
+                                       const float* __restrict__ weights, T* __restrict__ out, int width, int top,
+                                       const int* __restrict__ ids, const T* __restrict__ x, int experts,
+                                       const T* __restrict__ extra) {
     overlap_trigger();
     overlap_wait();
     const int token = blockIdx.x;
-    if (width % 4 == 0 && (((uintptr_t)rows | (uintptr_t)out) & 15) == 0) {
+    // A pair without a row: an identity expert where its number lies behind the experts that have matrices
+    // (its output is the token's own input row), else nothing.
+    if (width % 4 == 0 && (((uintptr_t)rows | (uintptr_t)out | (uintptr_t)x | (uintptr_t)extra) & 15) == 0) {
         // four columns a thread and step: the same sums in the same order, fewer and wider loads
         for (int i = threadIdx.x * 4; i < width; i += blockDim.x * 4) {
             float4 sum = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
             for (int j = 0; j < top; ++j) {
                 const int row = position[(size_t)token * top + j];
-                if (row < 0) continue;
+                if (row < 0 && !(x != nullptr && ids[(size_t)token * top + j] >= experts)) continue;
                 const float w = weights[(size_t)token * top + j];
-                const float4 v = load_four(rows + (size_t)row * width + i);
+                const float4 v = row < 0 ? load_four(x + (size_t)token * width + i) : load_four(rows + (size_t)row * width + i);
                 sum.x = fmaf(w, v.x, sum.x); sum.y = fmaf(w, v.y, sum.y);
                 sum.z = fmaf(w, v.z, sum.z); sum.w = fmaf(w, v.w, sum.w);
+            }
+            if (extra != nullptr) {
+                const float4 v = load_four(extra + (size_t)token * width + i);
+                sum.x += v.x; sum.y += v.y; sum.z += v.z; sum.w += v.w;
             }
             store_four(out + (size_t)token * width + i, sum);
         }
@@ -214,7 +241,10 @@ __global__ void combine_experts_kernel(const T* __restrict__ rows, const int* __
         for (int j = 0; j < top; ++j) {
             const int row = position[(size_t)token * top + j];
             if (row >= 0) sum = fmaf(weights[(size_t)token * top + j], to_float(rows[(size_t)row * width + i]), sum);
+            else if (x != nullptr && ids[(size_t)token * top + j] >= experts)
+                sum = fmaf(weights[(size_t)token * top + j], to_float(x[(size_t)token * width + i]), sum);
         }
+        if (extra != nullptr) sum += to_float(extra[(size_t)token * width + i]);
         out[(size_t)token * width + i] = from_float<T>(sum);
     }
 }
@@ -630,6 +660,25 @@ __device__ __forceinline__ float gelu_tanh_fn(float z) {
     return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
 }
 
+// out = gelu_tanh(gate) * up for rows [gate | up]
+template <typename T>
+__global__ void gelu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter) {
+    overlap_trigger();
+    overlap_wait();
+    const size_t token = blockIdx.x;
+    const T* row = gate_up + token * 2 * (size_t)inter;
+    if (inter % 4 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
+        for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4; i < inter; i += gridDim.y * blockDim.x * 4) {
+            const float4 gv = load_four(row + i), uv = load_four(row + inter + i);
+            store_four(out + token * inter + i, make_float4(gelu_tanh_fn(gv.x) * uv.x, gelu_tanh_fn(gv.y) * uv.y,
+                                                            gelu_tanh_fn(gv.z) * uv.z, gelu_tanh_fn(gv.w) * uv.w));
+        }
+        return;
+    }
+    for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < inter; i += gridDim.y * blockDim.x)
+        out[token * inter + i] = from_float<T>(gelu_tanh_fn(to_float(row[i])) * to_float(row[inter + i]));
+}
+
 template <typename T>
 __global__ void gelu_gate_rows_kernel(const T* __restrict__ gate, const T* __restrict__ table,
                                       const int* __restrict__ ids, T* __restrict__ out, int dim, int table_stride,
@@ -653,7 +702,8 @@ __global__ void gelu_gate_rows_kernel(const T* __restrict__ gate, const T* __res
 // choice scores stay eligible (group_count <= 1 or group_keep >= group_count: all do).
 B200_EXPORT int b200_route_experts(const void* x, const float* router, const float* correction, int* ids,
                                    float* weights, int tokens, int K, int E, int top, int group_count,
-                                   int group_keep, int group_top, int dtype, cudaStream_t stream) {
+                                   int group_keep, int group_top, int softmax_scores, int renormalise, int dtype,
+                                   cudaStream_t stream) {
     using namespace b200;
     if (tokens == 0) return 0;
     if (E <= 0 || top <= 0 || top > E || K <= 0) return fail("route_experts", "sizes out of range");
@@ -668,10 +718,12 @@ B200_EXPORT int b200_route_experts(const void* x, const float* router, const flo
     const int threads = (tokens <= 4 * kOverlapMostRows && E > 4) ? 256 : 128;
     if (dtype == 0)
         launch_overlapped_if(tokens <= kOverlapMostRows, route_experts_kernel<float>, tokens, threads, smem, stream,
-            (const float*)x, router, correction, ids, weights, K, E, top, group_count, group_keep, group_top);
+            (const float*)x, router, correction, ids, weights, K, E, top, group_count, group_keep, group_top,
+            softmax_scores, renormalise);
     else if (dtype == 1)
         launch_overlapped_if(tokens <= kOverlapMostRows, route_experts_kernel<__nv_bfloat16>, tokens, threads, smem, stream,
-            (const __nv_bfloat16*)x, router, correction, ids, weights, K, E, top, group_count, group_keep, group_top);
+            (const __nv_bfloat16*)x, router, correction, ids, weights, K, E, top, group_count, group_keep, group_top,
+            softmax_scores, renormalise);
     else
         return fail("route_experts", "dtype must be 0 (float32) or 1 (bfloat16)");
     return check_launch("route_experts");
@@ -702,17 +754,22 @@ B200_EXPORT int b200_gather_rows(const void* x, const int* index, int divisor, v
     return check_launch("gather_rows");
 }
 
+// ids, x, experts: pairs whose expert number is `experts` or more are identity experts, whose output is the
+// token's row of x (both null: there are none).  extra [tokens, width] or null: rows added to every token's sum.
 B200_EXPORT int b200_combine_experts(const void* rows, const int* position, const float* weights, void* out,
-                                     int tokens, int width, int top, int dtype, cudaStream_t stream) {
+                                     int tokens, int width, int top, const int* ids, const void* x, int experts,
+                                     const void* extra, int dtype, cudaStream_t stream) {
     using namespace b200;
     if (tokens == 0) return 0;
+    if ((ids == nullptr) != (x == nullptr)) return fail("combine_experts", "identity experts need the choices and the inputs");
     const int threads = width >= 1024 ? 256 : 128;
     if (dtype == 0)
         launch_overlapped_if(tokens <= kOverlapMostRows, combine_experts_kernel<float>, tokens, threads, 0, stream,
-            (const float*)rows, position, weights, (float*)out, width, top);
+            (const float*)rows, position, weights, (float*)out, width, top, ids, (const float*)x, experts, (const float*)extra);
     else if (dtype == 1)
         launch_overlapped_if(tokens <= kOverlapMostRows, combine_experts_kernel<__nv_bfloat16>, tokens, threads, 0, stream,
-            (const __nv_bfloat16*)rows, position, weights, (__nv_bfloat16*)out, width, top);
+            (const __nv_bfloat16*)rows, position, weights, (__nv_bfloat16*)out, width, top, ids, (const __nv_bfloat16*)x, experts,
+            (const __nv_bfloat16*)extra);
     else
         return fail("combine_experts", "dtype must be 0 (float32) or 1 (bfloat16)");
     return check_launch("combine_experts");
@@ -782,6 +839,21 @@ B200_EXPORT int b200_capped_swish_mul(const void* gate_up, void* out, int tokens
     else
         return fail("capped_swish_mul", "dtype must be 0 (float32) or 1 (bfloat16)");
     return check_launch("capped_swish_mul");
+}
+
+B200_EXPORT int b200_gelu_mul(const void* gate_up, void* out, int tokens, int inter, int dtype, cudaStream_t stream) {
+    using namespace b200;
+    if (tokens == 0 || inter == 0) return 0;
+    const dim3 grid(tokens, tokens >= 512 ? 1 : min(8, (inter + 1023) / 1024));
+    if (dtype == 0)
+        launch_overlapped_if(tokens <= kOverlapMostRows, gelu_mul_kernel<float>, grid, 256, 0, stream,
+            (const float*)gate_up, (float*)out, inter);
+    else if (dtype == 1)
+        launch_overlapped_if(tokens <= kOverlapMostRows, gelu_mul_kernel<__nv_bfloat16>, grid, 256, 0, stream,
+            (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter);
+    else
+        return fail("gelu_mul", "dtype must be 0 (float32) or 1 (bfloat16)");
+    return check_launch("gelu_mul");
 }
 
 B200_EXPORT int b200_gelu_gate_rows(const void* gate, const void* table, const int* ids, void* out, int tokens,

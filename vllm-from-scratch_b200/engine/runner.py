@@ -70,7 +70,8 @@ class ModelRunner:
                                     self.max_requests, self.dtype, self.device,
                                     embedding_need=self.model.embedding.cache_need())
         self.manager = CacheManager(self.storage.group_windows, page_size, num_pages, self.max_requests,
-                                    self.enable_prefix_caching, has_state=self.storage.has_state)
+                                    self.enable_prefix_caching, has_state=self.storage.has_state,
+                                    group_keep_first=self.storage.group_keep_first)
         self.step_function = StepFunction(self.model, self.storage, self.manager)
 
     def pages_that_fit(self, page_size: int, gpu_memory_utilization: float = 0.9,

@@ -21,21 +21,24 @@ GATE_NONE, GATE_SILU, GATE_CAPPED = 0, 1, 2
 
 def route_experts(x: torch.Tensor, router: torch.Tensor, correction: torch.Tensor | None, ids: torch.Tensor,
                   weights: torch.Tensor, top: int, group_count: int = 1, group_keep: int = 1,
-                  group_top: int = 2) -> None:
+                  group_top: int = 2, scoring: str = "sigmoid", renormalise: bool = False) -> None:
     """For every row of ``x`` ``[T, K]``: logits ``router @ x`` in float32 (``router`` float32 ``[E, K]``),
-    scores = sigmoid; the ``top`` experts with the largest ``score + correction`` among the experts of
+    scores = sigmoid of each (``scoring="softmax"``: the softmax over all E of them; ``renormalise``: the
+    weights are the chosen scores divided by their sum + 1e-20); the ``top`` experts with the largest ``score + correction`` among the experts of
     the ``group_keep`` best of ``group_count`` equal groups of neighbours (a group's mark: the sum of its
     ``group_top`` largest ``score + correction``) go to ``ids`` (int32 ``[T, top]``), their plain scores
     to ``weights`` (float32 ``[T, top]``).  Ties go to the smaller index."""
     tokens, k = x.shape
     experts = router.shape[0]
+    if scoring not in ("sigmoid", "softmax"):
+        raise KernelError(f"router scores {scoring!r}: 'sigmoid' or 'softmax'")
     _run("grouped", "b200_route_experts",
          _P(_check("router input", x, _RUN)), _P(_check("router matrix", router, torch.float32, (experts, k))),
          _P(_check("score correction", correction, torch.float32, (experts,), optional=True)),
          _P(_check("chosen experts", ids, torch.int32, (tokens, top))),
          _P(_check("weights of the chosen", weights, torch.float32, (tokens, top))),
          _I(tokens), _I(k), _I(experts), _I(top), _I(group_count), _I(group_keep), _I(group_top),
-         _I(_code(x.dtype)), _stream())
+         _I(1 if scoring == "softmax" else 0), _I(1 if renormalise else 0), _I(_code(x.dtype)), _stream())
 
 
 def expert_lists(ids: torch.Tensor, experts: int, offsets: torch.Tensor, sorted_pair: torch.Tensor,
@@ -58,14 +61,26 @@ def gather_rows(x: torch.Tensor, index: torch.Tensor, divisor: int, out: torch.T
          _I(rows), _I(width), _I(_code(x.dtype)), _stream())
 
 
-def combine_experts(rows: torch.Tensor, position: torch.Tensor, weights: torch.Tensor, out: torch.Tensor) -> None:
-    """``out[t] = sum_j weights[t, j] * rows[position[t * top + j]]`` in float32, j in order."""
+def combine_experts(rows: torch.Tensor, position: torch.Tensor, weights: torch.Tensor, out: torch.Tensor,
+                    identity: tuple[torch.Tensor, torch.Tensor, int] | None = None,
+                    extra: torch.Tensor | None = None) -> None:
+    """``out[t] = sum_j weights[t, j] * rows[position[t * top + j]]`` in float32, j in order (a pair whose
+    position is negative adds nothing).  ``identity = (ids, x, experts)``: a pair whose expert number ``ids[t, j]``
+    is ``experts`` or more belongs to an identity expert and adds ``weights[t, j] * x[t]``.  ``extra`` ``[T,
+    width]``: rows added to every token's sum (an expert that every token passes)."""
     tokens, width = out.shape
     top = weights.shape[1]
+    ids = x = experts = 0
+    if identity is not None:
+        ids = _check("chosen experts", identity[0], torch.int32, (tokens, top))
+        x = _check("expert input", identity[1], out.dtype, (tokens, width))
+        experts = int(identity[2])
     _run("grouped", "b200_combine_experts", _P(_check("expert rows", rows, out.dtype, (None, width))),
          _P(_check("rows of the pairs", position, torch.int32, (tokens * top,))),
          _P(_check("weights", weights, torch.float32, (tokens, top))), _P(_check("combined output", out, _RUN)),
-         _I(tokens), _I(width), _I(top), _I(_code(out.dtype)), _stream())
+         _I(tokens), _I(width), _I(top), _P(ids), _P(x), _I(experts),
+         _P(_check("rows added to every sum", extra, out.dtype, (tokens, width), optional=True)),
+         _I(_code(out.dtype)), _stream())
 
 
 def _gate(gated) -> tuple[int, float, float, float]:
@@ -123,6 +138,14 @@ def capped_swish_mul(gate_up: torch.Tensor, out: torch.Tensor, limit: float | No
     _run("grouped", "b200_capped_swish_mul", _P(_check("gate_up", gate_up, out.dtype, (tokens, 2 * inter))),
          _P(_check("activation output", out, _RUN)), _I(tokens), _I(inter),
          _F(math.inf if limit is None else limit), _F(slope), _F(offset), _I(_code(out.dtype)), _stream())
+
+
+def gelu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    """``out = gelu_tanh(gate_up[:, :I]) * gate_up[:, I:]`` in float32, with ``gelu_tanh(z) = z / 2 * (1 +
+    tanh(sqrt(2 / pi) * (z + 0.044715 z^3)))``."""
+    tokens, inter = out.shape
+    _run("grouped", "b200_gelu_mul", _P(_check("gate_up", gate_up, out.dtype, (tokens, 2 * inter))),
+         _P(_check("activation output", out, _RUN)), _I(tokens), _I(inter), _I(_code(out.dtype)), _stream())
 
 
 def gelu_gate_rows(gate: torch.Tensor, table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor,

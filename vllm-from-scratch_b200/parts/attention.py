@@ -225,3 +225,111 @@ class BiasedAttention(Mixer):
         out = torch.empty((tokens, self.env.hidden_size), dtype=x.dtype, device=x.device)
         kernels.gemm(attended, self.out_proj, out)
         return out
+
+
+@MIXERS.register("differential_attention")
+class DifferentialAttention(Mixer):
+    """Causal attention over a paged cache in which every head has two softmax maps over the same values, the
+    second subtracted from the first: with ``a_m = softmax_j(cap(q_m . k_mj * scale)) v_j`` for the maps m = 1, 2
+    (queries and keys of ``head_dim`` numbers each, laid out ``[map 1, map 2]`` head by head in the projections),
+    ``o = a1 - lam * a2``, then ``o * rsqrt(mean(o^2) + norm_eps) * (1 - diff)`` over the head's ``value_dim`` values,
+    then the output product over the heads side by side.  ``lam = exp(sum(lq1 * lk1)) - exp(sum(lq2 * lk2)) +
+    diff`` is one number for the layer, formed once from four vectors of ``head_dim`` numbers.
+
+    Scores are capped (``cap(s) = softcap * tanh(s / softcap)``; None: not capped); a query at position i sees the
+    keys ``j <= i`` with ``i - j < window`` and, whatever the window, the first ``keep_first`` positions of the
+    sequence, all at their true positions.  The position encoding (rotary family) rotates the first ``rotary_dim``
+    numbers of every map of every query and key head; the projections of queries, keys and values have biases
+    (``bias``, default True).  Grouped heads: query head h reads key/value head ``h // (num_heads //
+    num_kv_heads)``.  Scores, weights, the weighted sums, the difference and its norm are float32 in both run
+    modes.
+
+    params: ``num_heads``, ``num_kv_heads``, ``head_dim``, ``value_dim``, ``scale``, ``softcap``, ``window``,
+    ``keep_first`` (default 0), ``diff``, ``norm_eps``, ``bias``, ``weight_names`` (q, k, v, o matrices and the
+    vectors lq1, lk1, lq2, lk2; a bias is its matrix's name with ``bias_suffix``, default ``.b``, behind it)."""
+
+    graph_safe = True
+    MAPS = 2
+
+    def __init__(self, params: Mapping[str, Any], env: PartEnv, position: PositionEncoding) -> None:
+        super().__init__(params, env, position)
+        self.num_heads = int(params["num_heads"])
+        self.num_kv_heads = int(params["num_kv_heads"])
+        self.head_dim = int(params["head_dim"])
+        self.value_dim = int(params.get("value_dim") or self.head_dim)
+        self.scale = float(params.get("scale", self.head_dim ** -0.5))
+        softcap = params.get("softcap")
+        self.softcap = None if softcap is None else float(softcap)
+        window = params.get("window")
+        self.window = None if window is None else int(window)
+        self.keep_first = int(params.get("keep_first") or 0) if self.window is not None else 0
+        self.diff = float(params["diff"])
+        self.norm_eps = float(params["norm_eps"])
+        self.has_bias = bool(params.get("bias", True))
+        self.bias_suffix = str(params.get("bias_suffix", ".b"))
+        self.names = tuple(params.get("weight_names", ("q", "k", "v", "o", "lq1", "lk1", "lq2", "lk2")))
+        if self.num_heads % self.num_kv_heads:
+            raise ValueError(f"num_heads={self.num_heads} is not a multiple of num_kv_heads={self.num_kv_heads}")
+        if self.MAPS * self.head_dim > 1024 or self.value_dim > 512:
+            raise ValueError(f"head_dim={self.head_dim}, value_dim={self.value_dim}: maps up to 512 and values up to "
+                             f"512 are built")
+        if position.rotary_dim > self.head_dim:
+            raise ValueError(f"rotary_dim={position.rotary_dim} exceeds head_dim={self.head_dim}")
+        if self.window is not None and self.window <= 0:
+            raise ValueError(f"window must be positive, got {self.window}")
+        if self.softcap is not None and self.softcap <= 0:
+            raise ValueError(f"softcap must be positive, got {self.softcap}")
+        self.qkv = self.out_proj = self.bias = None
+        self.lam = 0.0
+
+    def expected_weights(self) -> dict[str, WeightInfo]:
+        hidden, d, dv, maps = self.env.hidden_size, self.head_dim, self.value_dim, self.MAPS
+        q, k, v, o = self.names[:4]
+        rows = {q: self.num_heads * maps * d, k: self.num_kv_heads * maps * d, v: self.num_kv_heads * dv}
+        names = {name: WeightInfo((count, hidden)) for name, count in rows.items()}
+        names[o] = WeightInfo((hidden, self.num_heads * dv))
+        if self.has_bias:
+            for name, count in rows.items():
+                names[name + self.bias_suffix] = WeightInfo((count,), "vector")
+        for name in self.names[4:]:
+            names[name] = WeightInfo((d,), "vector")
+        return names
+
+    def load_weights(self, tensors: Mapping[str, torch.Tensor]) -> None:
+        q, k, v, o, lq1, lk1, lq2, lk2 = self.names
+        self.qkv = torch.cat([tensors[q], tensors[k], tensors[v]], dim=0).contiguous()
+        self.out_proj = tensors[o].contiguous()
+        if self.has_bias:
+            self.bias = torch.cat([tensors[name + self.bias_suffix] for name in (q, k, v)]).contiguous()
+        first = torch.exp((tensors[lq1] * tensors[lk1]).sum())      # float32 vectors: one number, formed once
+        second = torch.exp((tensors[lq2] * tensors[lk2]).sum())
+        self.lam = float((first - second + self.diff).item())
+
+    def cache_need(self) -> KVPagesNeed:
+        # a position's keys of both maps lie side by side in one row of its key/value head
+        return KVPagesNeed(self.num_kv_heads, self.MAPS * self.head_dim, self.window, self.value_dim,
+                           keep_first=self.keep_first)
+
+    def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+        from ..kernels import differential
+        if cache.kind != "pages":
+            raise ValueError("differential attention needs a cache of pages")
+        group = ctx.groups[cache.group]
+        tokens = x.shape[0]
+        nq, nkv, d, dv = self.num_heads, self.num_kv_heads, self.head_dim, self.value_dim
+        qkv = torch.empty((tokens, self.qkv.shape[0]), dtype=x.dtype, device=x.device)
+        kernels.gemm(x, self.qkv, qkv)
+        q = torch.empty((tokens, nq * self.MAPS * d), dtype=x.dtype, device=x.device)
+        store = cache.writable
+        differential.bias_rope_cache(
+            qkv, self.bias, ctx.positions, group.slot_mapping, self.position.inverse_frequencies(),
+            self.position.rotary_dim, q, cache.keys if store else None, cache.values if store else None, nq, nkv, d, dv,
+            group.page_size)
+        attended = torch.empty((tokens, nq * dv), dtype=x.dtype, device=x.device)
+        differential.diff_paged_attention(
+            q, cache.keys, cache.values, attended, ctx.query_start, ctx.seq_lens, group.block_table, nq, nkv, d, dv,
+            group.page_size, self.scale, self.softcap, self.window, self.keep_first, self.lam, self.norm_eps,
+            1.0 - self.diff, ctx.max_query_len, ctx.max_seq_len, ctx.num_decode)
+        out = torch.empty((tokens, self.env.hidden_size), dtype=x.dtype, device=x.device)
+        kernels.gemm(attended, self.out_proj, out)
+        return out

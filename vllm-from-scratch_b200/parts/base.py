@@ -51,6 +51,9 @@ class KVPagesNeed:
     # then live in slabs of their own.  0: no values are kept at all, the cached rows serve as
     # keys and as values (``CacheView.values`` is then ``CacheView.keys``).
     value_dim: int | None = None
+    # With a window: the first ``keep_first`` positions of a sequence stay readable whatever the
+    # window, so the pages that hold them are never given back while the request lives.
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)
@@ -132,6 +135,27 @@ class NormedAddend:
     rows: torch.Tensor
     weight: torch.Tensor
     eps: float
+
+
+@dataclass
+class StreamAddend:
+    """Rows on their way into a residual that is kept as several streams ``X[T, S, H]``
+    (hyper-connections): all streams at once from the old ones, ``X'_t = sum_s mix[s, t] X_s +
+    out[t] rows``.  A block with several streams hands this to whatever reads the streams next
+    (the next sublayer's weighted sum and norm, the model's last norm over the plain sum), and
+    the update, the read and the norm run as one kernel."""
+
+    rows: torch.Tensor          # [T, H] in the run dtype
+    mix: torch.Tensor           # float32 [S, S], indexed [from, to]
+    out: torch.Tensor           # float32 [S]
+
+
+@dataclass
+class FreshStreams:
+    """The embedding's rows (float32 ``[T, H]``) that every stream of the residual is still to be
+    set to: what the first reader of the streams of a step is handed."""
+
+    rows: torch.Tensor
 
 
 @dataclass

@@ -15,7 +15,8 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
-from .base import BLOCKS, Block, CacheView, HalfNormedRows, Norm, NormedAddend, StepContext  # noqa: F401
+from .base import (BLOCKS, Block, CacheView, FreshStreams, HalfNormedRows, Norm, NormedAddend,  # noqa: F401
+                   StepContext, StreamAddend, WeightInfo)
 
 
 @BLOCKS.register("pre_norm")
@@ -126,3 +127,74 @@ class PostNormBlock(Block):
             rows = self._rows(pending, residual)
             pending = self.norms["post_side"].addend(self.side.forward(rows, ctx))
         return pending
+
+
+@BLOCKS.register("hyper_connections")
+class HyperConnectionBlock(Block):
+    """The pre-norm arrangement over a residual that is kept as ``streams`` copies ``X_1 .. X_S`` (float32 ``[T,
+    S, H]``, all equal to the embedding's rows at the start of the model).  For sublayer q (1: the mixer, 2: the
+    feed-forward) with its tensors ``in`` ``[S]``, ``out`` ``[S]`` and ``mix`` ``[S, S]`` (indexed ``[from, to]``)::
+
+        u = sum_s in[s] X_s;   y = sublayer(norm(u));   X_t <- sum_s mix[s, t] X_s + out[t] y   (all t at once)
+
+    What a sublayer returns travels on as a :class:`~.base.StreamAddend`, so that the update of the streams, the
+    weighted sum that the next sublayer reads (the next layer's, or the model's last norm over the plain sum)
+    and its RMSNorm are one kernel.  The norms must be plain RMSNorms (a weight and an eps).
+
+    params: ``streams``; ``names`` (the prefixes of the two sublayers' tensors; default ``hc1``, ``hc2``)."""
+
+    norm_roles = ("mixer", "feed_forward")
+    graph_safe = True
+    needs_feed_forward = False
+
+    def __init__(self, params, env, *, mixer, feed_forward, norms) -> None:
+        self.norm_roles = ("mixer", "feed_forward") if feed_forward is not None else ("mixer",)
+        super().__init__(params, env, mixer=mixer, feed_forward=feed_forward, norms=norms)
+        self.streams = int(params["streams"])
+        if self.streams < 1:
+            raise ValueError(f"block at {env.prefix!r}: streams={self.streams}")
+        self.names = tuple(params.get("names", ("hc1", "hc2")))[:len(self.norm_roles)]
+        for role, norm in self.norms.items():
+            if not hasattr(norm, "weight") or not hasattr(norm, "eps"):
+                raise ValueError(f"block at {env.prefix!r}: the norm in front of the {role} must be an RMSNorm")
+        self.tables: dict[str, torch.Tensor] = {}
+
+    def expected_weights(self) -> dict[str, WeightInfo]:
+        count = self.streams
+        names = {}
+        for name in self.names:
+            names[f"{name}.in"] = WeightInfo((count,), "vector")
+            names[f"{name}.out"] = WeightInfo((count,), "vector")
+            names[f"{name}.mix"] = WeightInfo((count, count), "vector")
+        return names
+
+    def load_weights(self, tensors) -> None:
+        self.tables = {name: tensor.contiguous() for name, tensor in tensors.items()}
+
+    def _read(self, pending, residual: torch.Tensor, name: str, norm) -> torch.Tensor:
+        """Apply what is pending to the streams, then the weighted sum under ``name`` and its norm."""
+        from ..kernels import streams
+        if isinstance(pending, FreshStreams):
+            update = {"fresh": pending.rows}
+        elif isinstance(pending, StreamAddend):
+            update = {"rows_in": pending.rows, "mix": pending.mix, "out_weights": pending.out}
+        else:
+            raise ValueError("a block over several streams takes what is handed to it as rows on their way into "
+                             "the streams (StreamAddend) or as the embedding's rows (FreshStreams)")
+        normed = torch.empty((residual.shape[0], residual.shape[2]), dtype=self.env.dtype, device=residual.device)
+        streams.stream_mix_norm(residual, **update, in_weights=self.tables[f"{name}.in"], norm_weight=norm.weight,
+                                eps=norm.eps, normed=normed)
+        return normed
+
+    def forward(self, x, residual: torch.Tensor, ctx: StepContext, cache: CacheView) -> StreamAddend:
+        if residual.dim() != 3 or residual.shape[1] != self.streams:
+            raise ValueError(f"block at {self.env.prefix!r} keeps {self.streams} streams, the residual is "
+                             f"{tuple(residual.shape)}")
+        first = self.names[0]
+        normed = self._read(x, residual, first, self.norms["mixer"])
+        pending = StreamAddend(self.mixer.forward(normed, ctx, cache), self.tables[f"{first}.mix"], self.tables[f"{first}.out"])
+        if self.feed_forward is None:
+            return pending
+        second = self.names[1]
+        normed = self._read(pending, residual, second, self.norms["feed_forward"])
+        return StreamAddend(self.feed_forward.forward(normed, ctx), self.tables[f"{second}.mix"], self.tables[f"{second}.out"])

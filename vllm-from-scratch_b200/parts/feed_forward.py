@@ -1,5 +1,5 @@
-"""Dense gated feed-forward: ``down(silu(gate(x)) * up(x))``, no biases
-(minivllm/models/qwen3.py:44-65).  ``gate`` and ``up`` are held as one matrix
+"""Dense gated feed-forward: ``down(silu(gate(x)) * up(x))`` (or with the tanh form of gelu on the
+gate), no biases (minivllm/models/qwen3.py:44-65).  ``gate`` and ``up`` are held as one matrix
 ``[2 I, H]`` with the gate rows first (minivllm/layers/linear.py:261-359), so one
 product serves both."""
 
@@ -17,13 +17,17 @@ from .base import FEED_FORWARDS, FeedForward, HalfNormedRows, Norm, PartEnv, Ste
 class GatedSiluFeedForward(FeedForward):
     """params: ``intermediate_size``; ``weight_names`` (the checkpoint's names of the gate, up and
     down matrices under the part's prefix; default ``gate_proj.weight``, ``up_proj.weight``,
-    ``down_proj.weight``)."""
+    ``down_proj.weight``); ``activation`` (of the gate: ``silu``, the default, or ``gelu_tanh``, ``z / 2 * (1
+    + tanh(sqrt(2 / pi) * (z + 0.044715 z^3)))``, in float32)."""
 
     graph_safe = True
 
     def __init__(self, params: Mapping[str, Any], env: PartEnv) -> None:
         super().__init__(params, env)
         self.intermediate_size = int(params["intermediate_size"])
+        self.activation = str(params.get("activation", "silu"))
+        if self.activation not in ("silu", "gelu_tanh"):
+            raise ValueError(f"gated feed-forward: activation {self.activation!r} ('silu' or 'gelu_tanh')")
         self.names = tuple(params.get("weight_names", ("gate_proj.weight", "up_proj.weight", "down_proj.weight")))
         self.gate_up: torch.Tensor | None = None
         self.down: torch.Tensor | None = None
@@ -39,7 +43,7 @@ class GatedSiluFeedForward(FeedForward):
         self.down = tensors[down].contiguous()
 
     def splits_norms(self, tokens: int) -> bool:
-        return (kernels.split_norm_ok(tokens, self.gate_up, fold=False, gated=True)
+        return (self.activation == "silu" and kernels.split_norm_ok(tokens, self.gate_up, fold=False, gated=True)
                 and kernels.split_norm_ok(tokens, self.down, fold=True))
 
     def forward(self, x: torch.Tensor | HalfNormedRows, ctx: StepContext,
@@ -48,7 +52,13 @@ class GatedSiluFeedForward(FeedForward):
         x = x.rows if isinstance(x, HalfNormedRows) else x
         tokens = x.shape[0]
         hidden = torch.empty((tokens, self.intermediate_size), dtype=x.dtype, device=x.device)
-        kernels.gated_silu_gemm(x, self.gate_up, hidden, scale=scale)
+        if self.activation == "silu":
+            kernels.gated_silu_gemm(x, self.gate_up, hidden, scale=scale)
+        else:
+            from ..kernels import grouped
+            gate_up = torch.empty((tokens, 2 * self.intermediate_size), dtype=x.dtype, device=x.device)
+            kernels.gemm(x, self.gate_up, gate_up)
+            grouped.gelu_mul(gate_up, hidden)
         out = torch.empty((tokens, self.env.hidden_size), dtype=x.dtype, device=x.device)
         if fold is None:
             kernels.gemm(hidden, self.down, out)
@@ -106,11 +116,14 @@ class CappedGatedFeedForward(FeedForward):
 @FEED_FORWARDS.register("routed_experts")
 class RoutedExperts(FeedForward):
     """A mixture of small gated feed-forwards, ``down_e(silu(gate_e x) * up_e x)``, of which every token uses
-    ``top``: router logits in float32, scores = sigmoid(logits); the choice is made on ``score + correction``
+    ``top``: router logits in float32, scores = sigmoid(logits) (``scoring="softmax"``: the softmax over all
+    router outputs); the choice is made on ``score + correction``
     (where the checkpoint has a correction), among the experts of the ``group_keep`` best of ``group_count``
     equal groups of neighbouring experts (a group's mark is the sum of its ``group_top`` largest choice
-    scores); the output is the sum of the chosen experts' outputs weighted with their plain scores, not
-    renormalised.
+    scores); the output is the sum of the chosen experts' outputs weighted with their plain scores
+    (``renormalise``: divided by their sum + 1e-20).  The last ``identity_experts`` router outputs have no
+    tensors: their expert's output is its input.  With ``shared_intermediate_size`` an expert of that width,
+    of the same form, runs for every token and is added unweighted.
 
     The tokens of a step are put into one list per expert on the device, the experts' products run as two
     grouped kernels over those lists (the first with the activation in its epilogue), and a last kernel adds
@@ -119,7 +132,11 @@ class RoutedExperts(FeedForward):
     params: ``num_experts``, ``top``, ``intermediate_size``, ``group_count`` (default 1), ``group_keep``
     (default ``group_count``), ``group_top`` (default 2), ``correction`` (default True), ``router_name``
     (default ``router``), ``correction_name`` (default ``correction``), ``expert_names`` (patterns with
-    ``{index}`` for gate, up, down; default ``e{index}.gate``, ``e{index}.up``, ``e{index}.down``)."""
+    ``{index}`` for gate, up, down; default ``e{index}.gate``, ``e{index}.up``, ``e{index}.down``), ``scoring``
+    (default ``sigmoid``), ``renormalise`` (default False), ``identity_experts`` (default 0; ``num_experts`` counts
+    the experts that have tensors, the router has ``num_experts + identity_experts`` outputs),
+    ``shared_intermediate_size`` (default None), ``shared_names`` (gate, up, down; default ``shared.gate``,
+    ``shared.up``, ``shared.down``)."""
 
     graph_safe = True
 
@@ -135,16 +152,27 @@ class RoutedExperts(FeedForward):
         self.router_name = str(params.get("router_name", "router"))
         self.correction_name = str(params.get("correction_name", "correction"))
         self.expert_names = tuple(params.get("expert_names", ("e{index}.gate", "e{index}.up", "e{index}.down")))
-        if not 1 <= self.top <= self.num_experts:
-            raise ValueError(f"top={self.top} of {self.num_experts} experts")
-        if self.group_count < 1 or self.num_experts % self.group_count:
-            raise ValueError(f"{self.num_experts} experts do not form {self.group_count} equal groups")
+        self.scoring = str(params.get("scoring", "sigmoid"))
+        self.renormalise = bool(params.get("renormalise", False))
+        self.identity_experts = int(params.get("identity_experts") or 0)
+        shared = params.get("shared_intermediate_size")
+        self.shared_intermediate_size = None if shared is None else int(shared)
+        self.shared_names = tuple(params.get("shared_names", ("shared.gate", "shared.up", "shared.down")))
+        self.router_outputs = self.num_experts + self.identity_experts
+        if self.scoring not in ("sigmoid", "softmax"):
+            raise ValueError(f"router scores {self.scoring!r}: 'sigmoid' or 'softmax'")
+        if self.identity_experts < 0 or self.num_experts < 1:
+            raise ValueError(f"{self.num_experts} experts and {self.identity_experts} identity experts")
+        if not 1 <= self.top <= self.router_outputs:
+            raise ValueError(f"top={self.top} of {self.router_outputs} experts")
+        if self.group_count < 1 or self.router_outputs % self.group_count:
+            raise ValueError(f"{self.router_outputs} experts do not form {self.group_count} equal groups")
         if not 1 <= self.group_keep <= self.group_count:
             raise ValueError(f"group_keep={self.group_keep} of {self.group_count} groups")
-        if self.top > self.group_keep * (self.num_experts // self.group_count):
+        if self.top > self.group_keep * (self.router_outputs // self.group_count):
             raise ValueError(f"top={self.top} experts cannot come from {self.group_keep} groups of "
-                             f"{self.num_experts // self.group_count}")
-        self.router = self.correction = self.gate_up = self.down = None
+                             f"{self.router_outputs // self.group_count}")
+        self.router = self.correction = self.gate_up = self.down = self.shared_gate_up = self.shared_down = None
 
     def _expert(self, index: int) -> tuple[str, str, str]:
         return tuple(pattern.format(index=index) for pattern in self.expert_names)
@@ -152,9 +180,14 @@ class RoutedExperts(FeedForward):
     def expected_weights(self) -> dict[str, WeightInfo]:
         inter, hidden = self.intermediate_size, self.env.hidden_size
         # the router's matrix is used in 32-bit arithmetic: kept in float32 like a norm's vector
-        names = {self.router_name: WeightInfo((self.num_experts, hidden), "vector")}
+        names = {self.router_name: WeightInfo((self.router_outputs, hidden), "vector")}
         if self.has_correction:
-            names[self.correction_name] = WeightInfo((self.num_experts,), "vector")
+            names[self.correction_name] = WeightInfo((self.router_outputs,), "vector")
+        if self.shared_intermediate_size is not None:
+            gate, up, down = self.shared_names
+            names[gate] = WeightInfo((self.shared_intermediate_size, hidden))
+            names[up] = WeightInfo((self.shared_intermediate_size, hidden))
+            names[down] = WeightInfo((hidden, self.shared_intermediate_size))
         for index in range(self.num_experts):
             gate, up, down = self._expert(index)
             names[gate] = WeightInfo((inter, hidden))
@@ -168,6 +201,10 @@ class RoutedExperts(FeedForward):
         names = [self._expert(index) for index in range(self.num_experts)]
         self.gate_up = torch.stack([torch.cat([tensors[gate], tensors[up]], dim=0) for gate, up, _ in names]).contiguous()
         self.down = torch.stack([tensors[down] for _, _, down in names]).contiguous()
+        if self.shared_intermediate_size is not None:
+            gate, up, down = self.shared_names
+            self.shared_gate_up = torch.cat([tensors[gate], tensors[up]], dim=0).contiguous()
+            self.shared_down = tensors[down].contiguous()
 
     # From this many rows over all lists on, bfloat16 products whose sizes the library takes go to it.
     LIBRARY_MIN_ROWS = 256
@@ -183,7 +220,7 @@ class RoutedExperts(FeedForward):
         ids = torch.empty((tokens, top), dtype=torch.int32, device=device)
         weights = torch.empty((tokens, top), dtype=torch.float32, device=device)
         grouped.route_experts(x, self.router, self.correction, ids, weights, top, self.group_count,
-                              self.group_keep, self.group_top)
+                              self.group_keep, self.group_top, scoring=self.scoring, renormalise=self.renormalise)
         # three words ahead of the offsets, so that offsets[1:] (where each list ends) begins at 16 bytes
         books = torch.empty(3 + experts + 1 + 2 * tokens * top, dtype=torch.int32, device=device)
         _, offsets, sorted_pair, position = torch.split(books, [3, experts + 1, tokens * top, tokens * top])
@@ -203,6 +240,15 @@ class RoutedExperts(FeedForward):
             rows = torch.empty((tokens * top, self.env.hidden_size), dtype=x.dtype, device=device)
             grouped.expert_gemm(x, self.gate_up, hidden, offsets, sorted_pair, top, gated="silu")
             grouped.expert_gemm(hidden, self.down, rows, offsets, None)
+        shared = None
+        if self.shared_gate_up is not None:
+            inner = torch.empty((tokens, self.shared_intermediate_size), dtype=x.dtype, device=device)
+            kernels.gated_silu_gemm(x, self.shared_gate_up, inner)
+            shared = torch.empty((tokens, self.env.hidden_size), dtype=x.dtype, device=device)
+            kernels.gemm(inner, self.shared_down, shared)
         out = torch.empty((tokens, self.env.hidden_size), dtype=x.dtype, device=device)
-        grouped.combine_experts(rows, position, weights, out)
+        # An identity expert's pairs have numbers past the lists' (no row: `position` is negative); the last
+        # kernel adds the token's own input for them, and the shared expert's row.
+        identity = (ids, x, experts) if self.identity_experts else None
+        grouped.combine_experts(rows, position, weights, out, identity=identity, extra=shared)
         return out

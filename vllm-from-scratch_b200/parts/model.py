@@ -16,7 +16,7 @@ import torch
 
 from .. import kernels
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, MIXERS, NORMS, OUTPUT_HEADS, POSITION_ENCODINGS, TOKEN_SIDES,
-                   Block, CacheView, KVPagesNeed, PartEnv, StateNeed, StepContext, WeightInfo)
+                   Block, CacheView, FreshStreams, KVPagesNeed, PartEnv, StateNeed, StepContext, WeightInfo)
 from .spec import LayerSpec, ModelSpec
 
 
@@ -146,14 +146,20 @@ class DecoderModel:
         receives ``(x, residual copy)`` after every layer execution, for looking inside."""
         tokens = token_ids.shape[0]
         residual = torch.empty((tokens, self.hidden_size), dtype=torch.float32, device=token_ids.device)
+        embedded = residual
+        if self.spec.streams is not None:
+            # Several streams: the embedding's rows travel to the first reader of the streams, whose
+            # kernel sets every stream to them on its way.
+            residual = torch.empty((tokens, self.spec.streams, self.hidden_size), dtype=torch.float32,
+                                   device=token_ids.device)
         ctx.token_ids = token_ids
         if embedding_cache is not None:
-            self.embedding.forward(token_ids, ctx, residual, self._token_error, cache=embedding_cache)
+            self.embedding.forward(token_ids, ctx, embedded, self._token_error, cache=embedding_cache)
         else:
             if self.embedding.cache_need() is not None:
                 raise ValueError("the embedding keeps state per request: hand its cache over (embedding_cache=)")
-            self.embedding.forward(token_ids, ctx, residual, self._token_error)
-        x = None
+            self.embedding.forward(token_ids, ctx, embedded, self._token_error)
+        x = None if self.spec.streams is None else FreshStreams(embedded)
         blocks = [self.layers[entry.layer] for entry in self.spec.schedule]
         for number, (block, cache) in enumerate(zip(blocks, caches)):
             # Two blocks that both say so for this many tokens split the norm between them: the

@@ -12,7 +12,7 @@ from typing import Any, Mapping
 import torch
 
 from .. import kernels
-from .base import NORMS, Norm, NormedAddend, PartEnv, WeightInfo
+from .base import NORMS, FreshStreams, Norm, NormedAddend, PartEnv, StreamAddend, WeightInfo
 
 
 @NORMS.register("rms_norm")
@@ -23,7 +23,9 @@ class RMSNorm(Norm):
     empty: the prefix itself is the tensor).
 
     ``forward`` also takes a :class:`~.base.NormedAddend` for ``x``: rows that pass through a norm of
-    their own on their way into the residual; both norms and the sum are then one kernel."""
+    their own on their way into the residual; both norms and the sum are then one kernel.  Where the
+    residual is kept as several streams (``[T, S, H]``), ``x`` is a :class:`~.base.StreamAddend` (or
+    :class:`~.base.FreshStreams`) and the norm reads the plain sum of the updated streams."""
 
     graph_safe = True
 
@@ -55,7 +57,12 @@ class RMSNorm(Norm):
         if out is None:
             count = residual.shape[0] if rows is None else rows.shape[0]
             out = torch.empty((count, self.size), dtype=self.env.dtype, device=residual.device)
-        if isinstance(x, NormedAddend):
+        if isinstance(x, (StreamAddend, FreshStreams)):
+            from ..kernels import streams
+            update = ({"fresh": x.rows} if isinstance(x, FreshStreams)
+                      else {"rows_in": x.rows, "mix": x.mix, "out_weights": x.out})
+            streams.stream_mix_norm(residual, **update, norm_weight=self.weight, eps=self.eps, normed=out, rows=rows)
+        elif isinstance(x, NormedAddend):
             kernels.add_normed_rmsnorm(x.rows, x.weight, x.eps, residual, self.weight, self.eps, out, rows)
         else:
             kernels.add_rmsnorm(x, residual, self.weight, self.eps, out, rows)

@@ -85,6 +85,10 @@ class ModelSpec:
     output_head: PartSpec
     # Tensor names that a checkpoint may carry and the model does not read.
     ignored_weights: tuple[str, ...] = ()
+    # Copies of the residual stream that the blocks keep (hyper-connections): the residual is then
+    # float32 ``[T, streams, hidden]``, every copy equal to the embedding's rows at the start, and the
+    # model's last norm reads their plain sum.  None: one stream ``[T, hidden]``.
+    streams: int | None = None
 
     def __post_init__(self) -> None:
         for index, entry in enumerate(self.schedule):
