@@ -576,7 +576,30 @@ def _lobuzen(layers: int, hidden: int, heads: int, inter: int, vocab: int) -> di
             "token_side": {"dim": 64}, "layers": made}
 
 
-DESIGNS = {"bemuzen": _bemuzen, "lobuzen": _lobuzen}
+def _nodopel(layers: int, hidden: int, heads: int, inter: int, vocab: int) -> dict:
+    """Layers of the sizes of a Qwen3 layer of this width.  The attention has the Qwen3 layer's heads, each as
+    two maps of 64 over values of 128 (so the four projections have the Qwen3 layer's shapes), a window of 1024
+    that keeps the first 4 positions, capped scores and stretched frequencies.  The feed-forwards alternate
+    between a dense one of the Qwen3 layer's width and a routed one: 2 of 8 experts of a quarter of that width
+    and 2 identity experts, beside a shared expert of half the width, so that a token passes through at most as
+    many feed-forward parameters as in the Qwen3 layer.  Three streams.  With three layers and more the second
+    runs twice in a row, so that ``layers`` counts the runs."""
+    mixer = {"heads": heads, "kv_heads": 8, "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "diff": 0.6, "softcap": 30.0,
+             "mask": {"size": 1024, "keep_first": 4},
+             "rot": {"dims": 64, "base": 1.0e6, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
+    dense = {"kind": "dense", "ff": inter}
+    moe = {"kind": "moe", "expert": {"ff": inter // 4}, "router": {"experts": 8, "identity": 2, "top": 2},
+           "shared": {"ff": inter // 2}}
+    looped = layers >= 3
+    made = [{"type": "attention", "mixer": mixer, "mlp": moe if index % 2 else dense}
+            for index in range(layers - 1 if looped else layers)]
+    raw = {"architecture": "Nodopel", "vocab": vocab, "width": hidden, "norm": {"eps": 1e-6}, "streams": 3, "layers": made}
+    if looped:
+        raw["loop"] = {"start": 1, "stop": 2, "times": 2}
+    return raw
+
+
+DESIGNS = {"bemuzen": _bemuzen, "lobuzen": _lobuzen, "nodopel": _nodopel}
 DESIGN_SIZES = {      # name -> (hidden, heads, feed-forward width)
     "1.7b-layers": (2048, 16, 6144),
     "8b-layers": (4096, 32, 12288),
@@ -842,7 +865,7 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (named in config)")
     parser.add_argument("--block-size", type=int, default=16)
     parser.add_argument("--no-points", action="store_true", help="the main point only")
-    parser.add_argument("--design", default=None, choices=("bemuzen", "lobuzen"),
+    parser.add_argument("--design", default=None, choices=("bemuzen", "lobuzen", "nodopel"),
                         help="instead of the default workload: layers of this design beside Qwen3 layers of equal sizes")
     args = parser.parse_args()
 
