@@ -534,3 +534,59 @@ def test_gelu_gate(dtype):
         want = plain.gelu_tanh(gate_up[:, :inter].double()) * gate_up[:, inter:].double()
         assert torch.allclose(out.cpu().double(), want, **(dict(rtol=1e-5, atol=1e-6) if dtype == torch.float32
                                                            else dict(rtol=1e-2, atol=1e-2)))
+
+
+@pytest.mark.parametrize("shape", [(4, 1, 48, 96, 96, 4, 16), (8, 2, 32, 64, None, 0, 16), (4, 2, 64, 128, 600, 3, 32),
+                                   (32, 1, 16, 16, 50, 2, 8), (2, 2, 80, 48, 1, 0, 16), (6, 2, 64, 128, 300, 300, 64)])
+def test_tensor_core_kernels_against_the_float32_arithmetic(shape):
+    """bfloat16 batches of decoding requests (lengths 1, the window's and the kept positions' edges, some with
+    their keys split over several blocks) ahead of portions of prompts (2, 63, 64, 65 and 200 tokens, with and
+    without a past): the tensor-core kernels against the float32 kernel on the same pages."""
+    from vllm_from_scratch_b200.kernels import differential
+    H, G, d, dv, window, keep, page = shape
+    g = torch.Generator().manual_seed(3)
+    edge = window if window is not None else 400
+    decoding = [1, 2, keep + 1, keep + 2, edge, edge + 1, edge + keep, edge + keep + 1, 900, 1500]
+    decoding = [n for n in decoding if n >= 1]
+    portions = [(2, 0), (63, 0), (64, 130), (65, 7), (200, edge + 3)]
+    lengths = decoding + [new + past for new, past in portions]
+    fresh = [1] * len(decoding) + [new for new, _ in portions]
+    pages_of = [-(-n // page) for n in lengths]
+    order = torch.randperm(sum(pages_of), generator=g).tolist()
+    tables, at = [], 0
+    for count in pages_of:
+        tables.append(order[at:at + count])
+        at += count
+    width = max(pages_of)
+    block_table = i32([t + [-1] * (width - len(t)) for t in tables])
+    k_pages = dev(torch.randn(len(order), G, page, 2 * d, generator=g), torch.bfloat16)
+    v_pages = dev(torch.randn(len(order), G, page, dv, generator=g), torch.bfloat16)
+    q = dev(torch.randn(sum(fresh), H * 2 * d, generator=g) * 2.0, torch.bfloat16)
+    starts = [0]
+    for new in fresh:
+        starts.append(starts[-1] + new)
+    outs = []
+    for tensor_cores, decode in ((False, 0), (True, len(decoding)), (True, 0)):
+        out = torch.zeros(sum(fresh), H * dv, dtype=torch.bfloat16, device="cuda")
+        differential.USE_TENSOR_CORES = tensor_cores
+        try:
+            differential.diff_paged_attention(q, k_pages, v_pages, out, i32(starts), i32(lengths), block_table, H, G, d,
+                                              dv, page, d ** -0.5, 20.0, window, keep, 0.45, 1e-6, 0.4,
+                                              max_query_len=max(fresh), max_seq_len=max(lengths), num_decode=decode)
+        finally:
+            differential.USE_TENSOR_CORES = True
+        outs.append(out.float().cpu())
+    assert differential.tensor_core_sizes_ok(d, dv)
+    for got in outs[1:]:
+        # outputs of root mean square 0.4, rounded to bfloat16: one step of the last place is 2 ** -8 at most
+        assert float((got - outs[0]).abs().max()) <= 2 ** -7, float((got - outs[0]).abs().max())
+
+
+def test_decode_splits_fill_the_gpu():
+    from vllm_from_scratch_b200.kernels.differential import decode_splits, tensor_core_sizes_ok
+    assert decode_splits(1, 1, 100, 148) == 1
+    assert decode_splits(1, 1, 5000, 148) == 16
+    assert decode_splits(8, 8, 1028, 148) == 4
+    assert decode_splits(64, 8, 4096, 148) == 1          # pairs that fill the GPU by themselves are not split
+    assert tensor_core_sizes_ok(48, 96) and tensor_core_sizes_ok(128, 256)
+    assert not tensor_core_sizes_ok(10, 6) and not tensor_core_sizes_ok(64, 512) and not tensor_core_sizes_ok(512, 64)

@@ -33,7 +33,13 @@ EXTRA_FLAGS: dict[str, list[str]] = {
 }
 LIBRARIES = ("norm", "rope_cache", "attention_generic", "gemm_f32", "attention_bf16", "gemm_bf16",
              "sampling", "decode_attention_static", "norm_ext", "attention_bias", "recurrence", "grouped", "streams",
-             "diff_attention")
+             "diff_attention", "diff_attention_bf16")
+# Sources that are compiled for given sizes (``-DNAME=value``): a model builds the sizes that its layers have when
+# it first runs them; the ones listed here are built with everything else.
+Defines = tuple[tuple[str, int], ...]
+DEFAULT_VARIANTS: dict[str, list[Defines]] = {
+    "diff_attention_bf16": [(("B200_DIFF_D", 64), ("B200_DIFF_DV", 128))],
+}
 
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -55,8 +61,15 @@ def _nvcc() -> str:
         "from source for sm_100a and there is no other code path")
 
 
-def _flags(name: str) -> list[str]:
-    return NVCC_FLAGS + EXTRA_FLAGS.get(name, [])
+def _flags(name: str, defines: Defines = ()) -> list[str]:
+    return NVCC_FLAGS + EXTRA_FLAGS.get(name, []) + [f"-D{key}={int(value)}" for key, value in defines]
+
+
+def _key(name: str, defines: Defines = ()) -> str:
+    """Name of a library in files and in this process: the source's, and the sizes it is compiled for."""
+    if not defines:
+        return name
+    return name + "+" + "_".join(f"{key.lower().removeprefix('b200_')}{int(value)}" for key, value in defines)
 
 
 def _build_dir() -> Path:
@@ -76,18 +89,18 @@ def _build_dir() -> Path:
     raise KernelBuildError(f"no writable folder for built kernels among {candidates}")
 
 
-def _digest(name: str) -> str:
+def _digest(name: str, defines: Defines = ()) -> str:
     h = hashlib.sha256()
     h.update((SOURCE_DIR / f"{name}.cu").read_bytes())
     for header in sorted([*SOURCE_DIR.glob("*.cuh"), *SOURCE_DIR.glob("*.h")]):
         h.update(header.read_bytes())
-    h.update(" ".join(_flags(name)).encode())
+    h.update(" ".join(_flags(name, defines)).encode())
     return h.hexdigest()[:16]
 
 
-def library_path(name: str) -> Path | None:
+def library_path(name: str, defines: Defines = ()) -> Path | None:
     """Path of the built library for the current sources, if it exists anywhere."""
-    file_name = f"{name}-{_digest(name)}.so"
+    file_name = f"{_key(name, defines)}-{_digest(name, defines)}.so"
     for folder in (SOURCE_DIR / "_build", Path(tempfile.gettempdir()) / f"b200_kernels_{os.getuid()}"):
         if (folder / file_name).is_file():
             return folder / file_name
@@ -97,20 +110,22 @@ def library_path(name: str) -> Path | None:
     return None
 
 
-def compile_library(name: str, verbose: bool = True) -> Path:
+def compile_library(name: str, verbose: bool = True, defines: Defines = ()) -> Path:
     source = SOURCE_DIR / f"{name}.cu"
     if not source.is_file():
         raise KernelBuildError(f"no kernel source {source}")
-    existing = library_path(name)
+    existing = library_path(name, defines)
     if existing is not None:
         return existing
     folder = _build_dir()
-    target = folder / f"{name}-{_digest(name)}.so"
-    scratch = folder / f".{name}-{os.getpid()}-{threading.get_ident()}.so"
-    command = [_nvcc(), *_flags(name), "-I", str(SOURCE_DIR), "-o", str(scratch), str(source)]
+    key = _key(name, defines)
+    target = folder / f"{key}-{_digest(name, defines)}.so"
+    scratch = folder / f".{key}-{os.getpid()}-{threading.get_ident()}.so"
+    command = [_nvcc(), *_flags(name, defines), "-I", str(SOURCE_DIR), "-o", str(scratch), str(source)]
     started = time.time()
     if verbose:
-        print(f"[b200 kernels] compiling {name}.cu for sm_100a ...", file=sys.stderr, flush=True)
+        sizes = " (" + ", ".join(f"{k}={v}" for k, v in defines) + ")" if defines else ""
+        print(f"[b200 kernels] compiling {name}.cu{sizes} for sm_100a ...", file=sys.stderr, flush=True)
     process = subprocess.Popen(command, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
     while True:
         try:
@@ -130,18 +145,20 @@ def compile_library(name: str, verbose: bool = True) -> Path:
     return target
 
 
-def load_library(name: str) -> ctypes.CDLL:
-    """The loaded library ``name``; compiled first if its build is missing."""
-    library = _loaded.get(name)
+def load_library(name: str, defines: Defines = ()) -> ctypes.CDLL:
+    """The loaded library ``name`` (compiled for the sizes ``defines``, pairs of a macro's name and its value, where
+    the source takes some); compiled first if its build is missing."""
+    key = _key(name, defines)
+    library = _loaded.get(key)
     if library is not None:
         return library
     with _lock:
-        library = _loaded.get(name)
+        library = _loaded.get(key)
         if library is None:
-            path = compile_library(name)
+            path = compile_library(name, defines=defines)
             library = ctypes.CDLL(str(path))
             library.b200_last_error.restype = ctypes.c_char_p
-            _loaded[name] = library
+            _loaded[key] = library
     return library
 
 
@@ -153,13 +170,15 @@ def is_loaded(name: str) -> bool:
 def compile_all(verbose: bool = True) -> list[Path]:
     """Build every kernel library that has a source file (several at a time)."""
     from concurrent.futures import ThreadPoolExecutor
-    names = [name for name in LIBRARIES if (SOURCE_DIR / f"{name}.cu").is_file()]
+    names = [(name, defines) for name in LIBRARIES if (SOURCE_DIR / f"{name}.cu").is_file()
+             for defines in DEFAULT_VARIANTS.get(name, [()])]
     with ThreadPoolExecutor(max_workers=min(8, len(names) or 1)) as pool:
-        built = list(pool.map(lambda n: compile_library(n, verbose), names))
+        built = list(pool.map(lambda n: compile_library(n[0], verbose, n[1]), names))
     # Libraries of earlier versions of the sources are of no use to anyone: drop them.
     current = {path.name for path in built}
     for path in {p.parent for p in built}:
         for stale in path.glob("*.so"):
+            # (a library compiled for sizes other than the default ones may be current all the same: it stays)
             if stale.name not in current and stale.name.split("-")[0] in LIBRARIES:
                 try:
                     stale.unlink()

@@ -8,10 +8,53 @@ from __future__ import annotations
 
 import torch
 
-from . import _F, _I, _P, KernelError, _check, _code, _run, _stream
+from ..csrc.build import load_library
+from . import _F, _I, _P, KernelError, _check, _code, _run, _stream, count_launch
 
 _RUN = (torch.float32, torch.bfloat16)
 MAPS = 2
+# bfloat16 batches go to the tensor-core kernels where their sizes allow (False: the float32 kernel for everything).
+USE_TENSOR_CORES = True
+SHARED_MEMORY_LIMIT = 200 * 1024
+
+
+_sms: dict[int, int] = {}
+
+
+def _sm_count(device: torch.device) -> int:
+    index = device.index if device.index is not None else torch.cuda.current_device()
+    if index not in _sms:
+        _sms[index] = int(torch.cuda.get_device_properties(index).multi_processor_count)
+    return _sms[index]
+
+
+def tensor_core_sizes_ok(head_dim: int, value_dim: int) -> bool:
+    """Whether ``csrc/diff_attention_bf16.cu`` can be compiled for these sizes: multiples of 16, the value head at
+    most 256 (a thread's registers hold its part of an output row), and two stages of a tile of 64 keys and values,
+    as well as the decode kernel's room for its warps' partial results, within a block's shared memory."""
+    if head_dim % 16 or value_dim % 16 or head_dim <= 0 or not 0 < value_dim <= 256:
+        return False
+    stages = 2 * 64 * ((MAPS * head_dim + 8) + (value_dim + 8)) * 2
+    merge = (8 * 16 * value_dim + 8 * 16 * 2 + 2 * 16 * value_dim) * 4
+    return max(stages, merge) <= SHARED_MEMORY_LIMIT
+
+
+def decode_splits(num_requests: int, num_kv_heads: int, keys: int, sms: int) -> int:
+    """Over how many blocks the keys of one (request, key/value head) of a decode batch are split: at least 256
+    keys to a block, at most 16 blocks, and so many that the blocks fill whole rounds of the GPU (two blocks to an
+    SM at a time) as nearly as possible; a split more costs a little.  Pairs that fill the GPU by themselves are
+    not split."""
+    pairs = max(1, num_requests * num_kv_heads)
+    slots = 2 * sms
+    if pairs >= slots:
+        return 1
+    best, best_fill = 1, 0.0
+    for splits in range(1, max(1, min(16, keys // 256)) + 1):
+        blocks = pairs * splits
+        fill = blocks / (-(-blocks // slots) * slots) - 0.002 * splits
+        if fill > best_fill:
+            best, best_fill = splits, fill
+    return best
 
 
 def bias_rope_cache(qkv: torch.Tensor, bias: torch.Tensor | None, positions: torch.Tensor, slots: torch.Tensor,
@@ -62,6 +105,31 @@ def diff_paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
         _check("block table", block_table, torch.int32, (requests, None)))
     if keep_first < 0:
         raise KernelError(f"keep_first={keep_first}")
+    if USE_TENSOR_CORES and dtype == torch.bfloat16 and tensor_core_sizes_ok(head_dim, value_dim):
+        # The tensor-core kernels, compiled for this pair of sizes: one-token requests at the head of the batch
+        # with their keys split over several blocks, portions of prompts in tiles of 64 queries.
+        decode = num_decode if num_q_heads // num_kv_heads <= 16 else 0
+        splits, partial_o, partial_ml = 1, None, None
+        if decode:
+            keys = max_seq_len if max_seq_len is not None else block_table.shape[1] * page_size
+            if window:
+                keys = min(keys, window + keep_first)
+            splits = decode_splits(decode, num_kv_heads, keys, _sm_count(q.device))
+            if splits > 1:
+                rows = decode * num_q_heads * MAPS * splits
+                partial_o = torch.empty((rows, value_dim), dtype=torch.float32, device=q.device)
+                partial_ml = torch.empty((rows, 2), dtype=torch.float32, device=q.device)
+        lib = load_library("diff_attention_bf16", (("B200_DIFF_D", head_dim), ("B200_DIFF_DV", value_dim)))
+        count_launch()
+        status = lib.b200_diff_attention_bf16(
+            *(_P(address) for address in checked), _I(requests), _I(tokens), _I(block_table.shape[1]),
+            _I(num_q_heads), _I(num_kv_heads), _I(page_size), _F(scale), _F(softcap or 0.0), _I(window or 0),
+            _I(keep_first), _F(lam), _F(eps), _F(out_scale), _I(decode), _I(splits),
+            _P(partial_o.data_ptr() if partial_o is not None else 0),
+            _P(partial_ml.data_ptr() if partial_ml is not None else 0), _stream())
+        if status != 0:
+            raise KernelError(lib.b200_last_error().decode())
+        return
     _run("diff_attention", "b200_diff_paged_attention", *(_P(address) for address in checked),
          _I(requests), _I(tokens), _I(block_table.shape[1]), _I(num_q_heads), _I(num_kv_heads), _I(head_dim),
          _I(value_dim), _I(page_size), _F(scale), _F(softcap or 0.0), _I(window or 0), _I(keep_first), _F(lam), _F(eps),
