@@ -20,63 +20,66 @@
 
 namespace b200 {
 
+// A block is one token and `units_per_block` of its units (a unit: one map of a query or key head, or a value
+// head), a warp per unit in turn.  The token's cosines and sines are formed once a block, in shared memory.
 template <typename T>
 __global__ void bias_rope_cache_kernel(const T* __restrict__ qkv, const float* __restrict__ bias,
                                        const int* __restrict__ positions, const int* __restrict__ slots,
                                        const float* __restrict__ inv_freq, T* __restrict__ q_out,
                                        T* __restrict__ k_pages, T* __restrict__ v_pages, int q_units, int k_units,
-                                       int v_heads, int maps, int d, int dv, int rotary_dim, int page_size) {
+                                       int v_heads, int maps, int d, int dv, int rotary_dim, int page_size,
+                                       int units_per_block) {
+    extern __shared__ float turn[];                 // [rotary_dim / 2] cosines, then as many sines
     overlap_trigger();
     overlap_wait();
     const int token = blockIdx.x;
     const int warps = blockDim.x >> 5;
-    const int unit = blockIdx.y * warps + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
-    if (unit >= q_units + k_units + v_heads) return;
+    const int half = rotary_dim >> 1;
+    const float position = (float)positions[token];
+    for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(position * inv_freq[j], &turn[half + j], &turn[j]);
+    __syncthreads();
+    const int units = q_units + k_units + v_heads;
+    const int first = blockIdx.y * units_per_block, last = min(units, first + units_per_block);
     const size_t width = (size_t)(q_units + k_units) * d + (size_t)v_heads * dv;
     const T* row = qkv + (size_t)token * width;
-    const bool is_q = unit < q_units;
-    int slot = 0;
-    if (!is_q) {
-        if (k_pages == nullptr) return;
-        slot = slots[token];
-        if (slot < 0) return;
-    }
-    const int page = slot / page_size, offset = slot - page * page_size;
-    if (unit >= q_units + k_units) {
-        const int head = unit - q_units - k_units;
-        const size_t column = (size_t)(q_units + k_units) * d + (size_t)head * dv;
-        T* dst = v_pages + (((size_t)page * v_heads + head) * page_size + offset) * dv;
-        for (int j = lane; j < dv; j += 32) {
+    const int slot = k_pages != nullptr ? slots[token] : -1;
+    const int page = slot >= 0 ? slot / page_size : 0, offset = slot >= 0 ? slot - page * page_size : 0;
+    for (int unit = first + (threadIdx.x >> 5); unit < last; unit += warps) {
+        const bool is_q = unit < q_units;
+        if (!is_q && slot < 0) continue;
+        if (unit >= q_units + k_units) {
+            const int head = unit - q_units - k_units;
+            const size_t column = (size_t)(q_units + k_units) * d + (size_t)head * dv;
+            T* dst = v_pages + (((size_t)page * v_heads + head) * page_size + offset) * dv;
+            for (int j = lane; j < dv; j += 32) {
+                float v = to_float(row[column + j]);
+                if (bias) v += bias[column + j];
+                dst[j] = from_float<T>(v);
+            }
+            continue;
+        }
+        const size_t column = (size_t)unit * d;
+        T* dst;
+        if (is_q) {
+            dst = q_out + (size_t)token * q_units * d + column;
+        } else {
+            const int ku = unit - q_units, heads = k_units / maps;
+            dst = k_pages + ((((size_t)page * heads + ku / maps) * page_size + offset) * maps + ku % maps) * d;
+        }
+        for (int j = lane; j < half; j += 32) {
+            float u = to_float(row[column + j]), v = to_float(row[column + j + half]);
+            if (bias) { u += bias[column + j]; v += bias[column + j + half]; }
+            float o1, o2;
+            rotate_pair(u, v, turn[j], turn[half + j], o1, o2);
+            dst[j] = from_float<T>(o1);
+            dst[j + half] = from_float<T>(o2);
+        }
+        for (int j = rotary_dim + lane; j < d; j += 32) {
             float v = to_float(row[column + j]);
             if (bias) v += bias[column + j];
             dst[j] = from_float<T>(v);
         }
-        return;
-    }
-    const size_t column = (size_t)unit * d;
-    T* dst;
-    if (is_q) {
-        dst = q_out + (size_t)token * q_units * d + column;
-    } else {
-        const int ku = unit - q_units, heads = k_units / maps;
-        dst = k_pages + ((((size_t)page * heads + ku / maps) * page_size + offset) * maps + ku % maps) * d;
-    }
-    const int half = rotary_dim >> 1;
-    const float position = (float)positions[token];
-    for (int j = lane; j < half; j += 32) {
-        float u = to_float(row[column + j]), v = to_float(row[column + j + half]);
-        if (bias) { u += bias[column + j]; v += bias[column + j + half]; }
-        float s, c, o1, o2;
-        sincosf(position * inv_freq[j], &s, &c);
-        rotate_pair(u, v, c, s, o1, o2);
-        dst[j] = from_float<T>(o1);
-        dst[j + half] = from_float<T>(o2);
-    }
-    for (int j = rotary_dim + lane; j < d; j += 32) {
-        float v = to_float(row[column + j]);
-        if (bias) v += bias[column + j];
-        dst[j] = from_float<T>(v);
     }
 }
 
@@ -295,17 +298,22 @@ B200_EXPORT int b200_bias_rope_cache(const void* qkv, const float* bias, const i
     if ((k_pages == nullptr) != (v_pages == nullptr)) return fail("bias_rope_cache", "key and value pages must be given together");
     if (k_pages && page_size <= 0) return fail("bias_rope_cache", "page_size must be positive");
     const int k_units = v_heads * maps;
-    const int warps = 4;
-    dim3 grid(num_tokens, (q_units + k_units + v_heads + warps - 1) / warps);
+    const int units = q_units + k_units + v_heads;
+    // Many tokens: a block takes all of a token's units, so that its cosines and sines are formed once; few tokens:
+    // a unit to a warp, so that the launch has blocks enough.
+    const int warps = 8;
+    const int units_per_block = num_tokens >= 256 ? units : warps;
+    dim3 grid(num_tokens, (units + units_per_block - 1) / units_per_block);
     if (grid.y > 65535) return fail("bias_rope_cache", "too many heads");
+    const size_t smem = sizeof(float) * (size_t)rotary_dim;
     if (dtype == 0)
-        launch_overlapped_if(num_tokens <= kOverlapMostRows, bias_rope_cache_kernel<float>, grid, warps * 32, 0, stream,
+        launch_overlapped_if(num_tokens <= kOverlapMostRows, bias_rope_cache_kernel<float>, grid, warps * 32, smem, stream,
             (const float*)qkv, bias, positions, slots, inv_freq, (float*)q_out, (float*)k_pages, (float*)v_pages,
-            q_units, k_units, v_heads, maps, d, dv, rotary_dim, page_size);
+            q_units, k_units, v_heads, maps, d, dv, rotary_dim, page_size, units_per_block);
     else if (dtype == 1)
-        launch_overlapped_if(num_tokens <= kOverlapMostRows, bias_rope_cache_kernel<__nv_bfloat16>, grid, warps * 32, 0, stream,
+        launch_overlapped_if(num_tokens <= kOverlapMostRows, bias_rope_cache_kernel<__nv_bfloat16>, grid, warps * 32, smem, stream,
             (const __nv_bfloat16*)qkv, bias, positions, slots, inv_freq, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pages,
-            (__nv_bfloat16*)v_pages, q_units, k_units, v_heads, maps, d, dv, rotary_dim, page_size);
+            (__nv_bfloat16*)v_pages, q_units, k_units, v_heads, maps, d, dv, rotary_dim, page_size, units_per_block);
     else
         return fail("bias_rope_cache", "dtype must be 0 (float32) or 1 (bfloat16)");
     return check_launch("bias_rope_cache");

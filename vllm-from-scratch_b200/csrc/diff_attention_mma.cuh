@@ -23,6 +23,7 @@ namespace b200 {
 
 constexpr int kDiffThreads = 256;
 constexpr int kDiffPad = 8;                     // bfloat16 elements behind every row of a tile
+constexpr int kDiffDecodeStages = 3;            // tiles of shared memory of a decode block
 
 struct DiffMmaArgs {
     const int* query_start;
@@ -89,6 +90,36 @@ __device__ __forceinline__ float capped_log2(float x, float cap, float inv_cap) 
     return cap * kLog2e * (1.0f - __fdividef(2.0f, e + 1.0f));
 }
 
+// o += P V for 16 entries of a tile: the weights as three bfloat16 pieces (smallest first), `v_row` this lane's
+// row and column half of the value tile for ldmatrix.  The products of one piece over all columns of the head
+// stand together, so that two products into the same accumulator have the others between them.
+template <int DV>
+__device__ __forceinline__ void weighted_values(float (&o)[DV / 8][4], const unsigned (&pa)[4], const unsigned (&pm)[4],
+                                                const unsigned (&pl)[4], const bf16* v_row) {
+    constexpr int kBlocks = DV / 16, kAtOnce = kBlocks % 4 == 0 ? 4 : kBlocks % 2 == 0 ? 2 : 1;
+#pragma unroll
+    for (int j0 = 0; j0 < kBlocks; j0 += kAtOnce) {
+        unsigned b[kAtOnce][4];
+#pragma unroll
+        for (int i = 0; i < kAtOnce; ++i) ldmatrix_x4_trans(b[i], v_row + (j0 + i) * 16);
+#pragma unroll
+        for (int i = 0; i < kAtOnce; ++i) {
+            mma_bf16(o[2 * (j0 + i)], pl, b[i][0], b[i][1]);
+            mma_bf16(o[2 * (j0 + i) + 1], pl, b[i][2], b[i][3]);
+        }
+#pragma unroll
+        for (int i = 0; i < kAtOnce; ++i) {
+            mma_bf16(o[2 * (j0 + i)], pm, b[i][0], b[i][1]);
+            mma_bf16(o[2 * (j0 + i) + 1], pm, b[i][2], b[i][3]);
+        }
+#pragma unroll
+        for (int i = 0; i < kAtOnce; ++i) {
+            mma_bf16(o[2 * (j0 + i)], pa, b[i][0], b[i][1]);
+            mma_bf16(o[2 * (j0 + i) + 1], pa, b[i][2], b[i][3]);
+        }
+    }
+}
+
 // A warp's 16 rows against a tile of 64 entries: scores of its map, softmax update, the product with the values.
 // `s` comes in as the raw products and is used up.
 template <int DV>
@@ -131,18 +162,7 @@ __device__ __forceinline__ void softmax_and_values(float (&s)[8][4], float (&o)[
         split_bf16x3(s[2 * kk][2], s[2 * kk][3], pa[1], pm[1], pl[1]);
         split_bf16x3(s[2 * kk + 1][0], s[2 * kk + 1][1], pa[2], pm[2], pl[2]);
         split_bf16x3(s[2 * kk + 1][2], s[2 * kk + 1][3], pa[3], pm[3], pl[3]);
-#pragma unroll
-        for (int j = 0; j < DV / 16; ++j) {
-            const int key = kk * 16 + (mi & 1) * 8 + ri;
-            unsigned b[4];
-            ldmatrix_x4_trans(b, v_s + key * (DV + kDiffPad) + (j * 2 + (mi >> 1)) * 8);
-            mma_bf16(o[2 * j], pl, b[0], b[1]);         // smallest pieces first
-            mma_bf16(o[2 * j + 1], pl, b[2], b[3]);
-            mma_bf16(o[2 * j], pm, b[0], b[1]);
-            mma_bf16(o[2 * j + 1], pm, b[2], b[3]);
-            mma_bf16(o[2 * j], pa, b[0], b[1]);
-            mma_bf16(o[2 * j + 1], pa, b[2], b[3]);
-        }
+        weighted_values<DV>(o, pa, pm, pl, v_s + (kk * 16 + (mi & 1) * 8 + ri) * (DV + kDiffPad) + (mi >> 1) * 8);
     }
 }
 
@@ -215,7 +235,7 @@ __host__ __device__ constexpr int diff_stage_elements() { return kKeys * (2 * D 
 // grid (query tiles, query heads).  A tile is 64 consecutive query tokens of one request, 16 to a warp of each
 // map; request r owns the tiles [(start[r] - offset) / 64 + r, (start[r + 1] - offset) / 64 + r + 1).
 template <int D, int DV>
-__global__ void __launch_bounds__(kDiffThreads, 2) diff_prefill_mma_kernel(
+__global__ void __launch_bounds__(kDiffThreads, DV <= 128 ? 2 : 1) diff_prefill_mma_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
     bf16* __restrict__ out, const DiffMmaArgs p) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -388,25 +408,27 @@ __global__ void __launch_bounds__(kDiffThreads) diff_decode_mma_kernel(
     auto k_stage = [&](int s) { return stage_base + (size_t)s * kStage; };
     auto v_stage = [&](int s) { return stage_base + (size_t)s * kStage + kKeys * (2 * D + kDiffPad); };
 
-    if (tiles > 0) {
-        load_list_tile<D, DV>(k_stage(0), v_stage(0), k_pages, v_pages, table, list, my_begin, my_end, kv_head, p.nkv,
-                              p.page_size);
+    // A decode block waits for memory and little else: two tiles are on their way while one is used (a group of
+    // copies is committed every turn, an empty one too, so that the count behind the wait is the same every turn).
+#pragma unroll
+    for (int s = 0; s < kDiffDecodeStages - 1; ++s) {
+        if (s < tiles)
+            load_list_tile<D, DV>(k_stage(s), v_stage(s), k_pages, v_pages, table, list, my_begin + s * kKeys, my_end,
+                                  kv_head, p.nkv, p.page_size);
         cp_async_commit();
     }
     const int mi = lane >> 3, ri = lane & 7;
     for (int t = 0; t < tiles; ++t) {
         const int e0 = my_begin + t * kKeys;
-        if (t + 1 < tiles) {
-            load_list_tile<D, DV>(k_stage((t + 1) & 1), v_stage((t + 1) & 1), k_pages, v_pages, table, list, e0 + kKeys,
-                                  my_end, kv_head, p.nkv, p.page_size);
-            cp_async_commit();
-            cp_async_wait<1>();
-        } else {
-            cp_async_wait<0>();
-        }
+        const int ahead = t + kDiffDecodeStages - 1;
+        if (ahead < tiles)
+            load_list_tile<D, DV>(k_stage(ahead % kDiffDecodeStages), v_stage(ahead % kDiffDecodeStages), k_pages, v_pages,
+                                  table, list, my_begin + ahead * kKeys, my_end, kv_head, p.nkv, p.page_size);
+        cp_async_commit();
+        cp_async_wait<kDiffDecodeStages - 1>();
         __syncthreads();
-        const bf16* k_map = k_stage(t & 1) + map * D;
-        const bf16* v_s = v_stage(t & 1);
+        const bf16* k_map = k_stage(t % kDiffDecodeStages) + map * D;
+        const bf16* v_s = v_stage(t % kDiffDecodeStages);
 
         float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
 #pragma unroll
@@ -453,19 +475,10 @@ __global__ void __launch_bounds__(kDiffThreads) diff_decode_mma_kernel(
         split_bf16x3(s[1][0], s[1][1], pa[2], pm[2], pl[2]);
         split_bf16x3(s[1][2], s[1][3], pa[3], pm[3], pl[3]);
 #pragma unroll
-        for (int j = 0; j < DV / 16; ++j) {
-            o[2 * j][0] *= alpha_a; o[2 * j][1] *= alpha_a; o[2 * j][2] *= alpha_b; o[2 * j][3] *= alpha_b;
-            o[2 * j + 1][0] *= alpha_a; o[2 * j + 1][1] *= alpha_a; o[2 * j + 1][2] *= alpha_b; o[2 * j + 1][3] *= alpha_b;
-            const int key = part * 16 + (mi & 1) * 8 + ri;
-            unsigned b[4];
-            ldmatrix_x4_trans(b, v_s + key * (DV + kDiffPad) + (j * 2 + (mi >> 1)) * 8);
-            mma_bf16(o[2 * j], pl, b[0], b[1]);         // smallest pieces first
-            mma_bf16(o[2 * j + 1], pl, b[2], b[3]);
-            mma_bf16(o[2 * j], pm, b[0], b[1]);
-            mma_bf16(o[2 * j + 1], pm, b[2], b[3]);
-            mma_bf16(o[2 * j], pa, b[0], b[1]);
-            mma_bf16(o[2 * j + 1], pa, b[2], b[3]);
+        for (int nt = 0; nt < DV / 8; ++nt) {
+            o[nt][0] *= alpha_a; o[nt][1] *= alpha_a; o[nt][2] *= alpha_b; o[nt][3] *= alpha_b;
         }
+        weighted_values<DV>(o, pa, pm, pl, v_s + (part * 16 + (mi & 1) * 8 + ri) * (DV + kDiffPad) + (mi >> 1) * 8);
         __syncthreads();
     }
 
@@ -576,7 +589,7 @@ __global__ void __launch_bounds__(128) diff_merge_splits_kernel(
 
 template <int D, int DV>
 constexpr int diff_decode_smem() {
-    constexpr int stages = 2 * diff_stage_elements<D, DV>() * (int)sizeof(bf16);
+    constexpr int stages = kDiffDecodeStages * diff_stage_elements<D, DV>() * (int)sizeof(bf16);
     constexpr int merge = (8 * 16 * DV + 8 * 16 * 2 + 2 * 16 * DV) * (int)sizeof(float);
     return stages > merge ? stages : merge;
 }

@@ -15,7 +15,7 @@ _RUN = (torch.float32, torch.bfloat16)
 MAPS = 2
 # bfloat16 batches go to the tensor-core kernels where their sizes allow (False: the float32 kernel for everything).
 USE_TENSOR_CORES = True
-SHARED_MEMORY_LIMIT = 200 * 1024
+SHARED_MEMORY_LIMIT = 220 * 1024
 
 
 _sms: dict[int, int] = {}
@@ -30,11 +30,11 @@ def _sm_count(device: torch.device) -> int:
 
 def tensor_core_sizes_ok(head_dim: int, value_dim: int) -> bool:
     """Whether ``csrc/diff_attention_bf16.cu`` can be compiled for these sizes: multiples of 16, the value head at
-    most 256 (a thread's registers hold its part of an output row), and two stages of a tile of 64 keys and values,
-    as well as the decode kernel's room for its warps' partial results, within a block's shared memory."""
+    most 256 (a thread's registers hold its part of an output row), and the decode kernel's three stages of a tile
+    of 64 keys and values, as well as its room for its warps' partial results, within a block's shared memory."""
     if head_dim % 16 or value_dim % 16 or head_dim <= 0 or not 0 < value_dim <= 256:
         return False
-    stages = 2 * 64 * ((MAPS * head_dim + 8) + (value_dim + 8)) * 2
+    stages = 3 * 64 * ((MAPS * head_dim + 8) + (value_dim + 8)) * 2
     merge = (8 * 16 * value_dim + 8 * 16 * 2 + 2 * 16 * value_dim) * 4
     return max(stages, merge) <= SHARED_MEMORY_LIMIT
 
@@ -108,7 +108,10 @@ def diff_paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
     if USE_TENSOR_CORES and dtype == torch.bfloat16 and tensor_core_sizes_ok(head_dim, value_dim):
         # The tensor-core kernels, compiled for this pair of sizes: one-token requests at the head of the batch
         # with their keys split over several blocks, portions of prompts in tiles of 64 queries.
-        decode = num_decode if num_q_heads // num_kv_heads <= 16 else 0
+        # one-token requests: all of a decode step, the first ``num_decode`` of a step that mixes them with prompts
+        decode = requests if max_query_len == 1 and tokens == requests else num_decode
+        if num_q_heads // num_kv_heads > 16:
+            decode = 0
         splits, partial_o, partial_ml = 1, None, None
         if decode:
             keys = max_seq_len if max_seq_len is not None else block_table.shape[1] * page_size
