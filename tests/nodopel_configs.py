@@ -61,8 +61,8 @@ ND_A = {
 ND_B = {
     "architecture": "Nodopel", "vocab": 211, "width": 128, "norm": {"eps": 1e-6}, "streams": 4,
     "layers": [
-        _layer(2, 1, 64, 128, 0.125, 0.6, _moe(32, 4, 2), window=50, keep=5, softcap=30.0,
-               rot=_rot(32, 50000.0, (4.0, 1.0, 4.0, 128))),
+        _layer(2, 1, 64, 128, 0.125, 0.55, _moe(32, 4, 2), window=50, keep=5, softcap=25.0,
+               rot=_rot(32, 40000.0, (6.0, 1.0, 4.0, 128))),
         _layer(2, 2, 64, 64, 0.125, 0.3, _dense(96), rot=_rot(64, 10000.0)),
         _layer(1, 1, 128, 256, 0.09, 0.7, _moe(16, 8, 4, identity=0, shared=64), window=70, keep=0, softcap=15.0),
         _layer(4, 2, 128, 128, 0.09, 0.4, _dense(64), window=17, keep=2, rot=_rot(64, 2000.0, (16.0, 2.0, 8.0, 256))),
@@ -83,14 +83,17 @@ ND_C = {
     ],
 }
 
-# No streams at all (a plain residual) and a loop over the first layer alone.
+# No streams at all (a plain residual), a loop over the first layer alone, layers without a feed-forward in the
+# middle and at the end.
 ND_D = {
     "architecture": "Nodopel", "vocab": 40, "width": 96, "norm": {"eps": 1e-5},
     "loop": {"start": 0, "stop": 1, "times": 3},
     "layers": [
         _layer(6, 3, 16, 16, 0.25, 0.45, _moe(24, 12, 3, identity=4, shared=40), window=40, keep=8, softcap=12.0,
                rot=_rot(16, 3000.0, (5.0, 1.0, 3.0, 32))),
+        _layer(3, 1, 16, 32, 0.25, 0.3, None, window=30, keep=2, rot=_rot(16, 700.0)),
         _layer(2, 1, 32, 48, 0.2, 0.75, _dense(120), window=64, keep=16, rot=_rot(8, 250.0)),
+        _layer(2, 2, 8, 12, 0.4, 0.15, None),
     ],
 }
 
@@ -100,11 +103,11 @@ ND_E = {
     "architecture": "Nodopel", "vocab": 500, "width": 384, "norm": {"eps": 1e-5}, "streams": 5,
     "loop": {"start": 1, "stop": 2, "times": 1},
     "layers": [
-        _layer(6, 3, 64, 64, 0.125, 0.6, _dense(448), window=100, keep=7, softcap=30.0,
+        _layer(6, 3, 64, 64, 0.125, 0.35, _dense(448), window=100, keep=7, softcap=35.0,
                rot=_rot(48, 20000.0, (8.0, 1.0, 4.0, 512))),
         _layer(12, 1, 32, 48, 0.18, 0.25, _moe(96, 16, 4, identity=8, shared=160), window=130, keep=33, softcap=40.0,
                rot=_rot(32, 5000.0)),
-        _layer(3, 3, 48, 96, 0.15, 0.5, _moe(160, 16, 6, identity=2), rot=_rot(16, 800.0, (2.0, 1.0, 4.0, 64))),
+        _layer(3, 3, 48, 80, 0.15, 0.5, _moe(160, 16, 6, identity=2), rot=_rot(16, 800.0, (2.0, 1.0, 4.0, 64))),
     ],
 }
 

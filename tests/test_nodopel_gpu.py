@@ -293,7 +293,7 @@ def test_streams_between_two_sublayers(dtype, shape):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("shape", [(4, 1, 48, 96, 24), (3, 3, 10, 6, 6), (2, 1, 64, 128, 0), (6, 2, 16, 24, 16), (1, 1, 128, 64, 2)])
+@pytest.mark.parametrize("shape", [(5, 1, 48, 80, 32), (3, 3, 10, 6, 6), (2, 1, 64, 128, 0), (6, 2, 16, 24, 16), (1, 1, 128, 64, 2)])
 def test_bias_rotation_and_pages(dtype, shape):
     """Biases, the rotation of the first numbers of every map of every head at far positions, keys and
     values into scattered slots; a token without a slot stores nothing."""
@@ -306,7 +306,7 @@ def test_bias_rotation_and_pages(dtype, shape):
     bias = torch.randn(width, generator=g)
     positions = [0, 1, 5, 1000, 77777, 31, 2]
     slots = [9, 2, -1, 23, 0, 14, 7]
-    rot = {"dims": rotary, "base": 10000.0, "scaling": {"factor": 4.0, "low": 1.0, "high": 4.0, "original": 64}}
+    rot = {"dims": rotary, "base": 10000.0, "scaling": {"factor": 6.0, "low": 1.0, "high": 3.0, "original": 64}}
     frequencies = plain.rotary_frequencies(rot) if rotary else []
     inv_freq = dev(torch.tensor(frequencies, dtype=torch.float64).float()) if rotary else None
     q_out = torch.zeros(tokens, H * 2 * d, dtype=dtype, device="cuda")
@@ -359,7 +359,7 @@ def paged(rows, page_size, pages_order, heads, size, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("shape", [(4, 1, 48, 96, 96, 4), (6, 3, 10, 6, 7, 9), (2, 2, 64, 128, 100, 1), (8, 2, 64, 64, 64, 0),
+@pytest.mark.parametrize("shape", [(5, 1, 48, 80, 90, 6), (6, 3, 10, 6, 7, 9), (2, 2, 64, 128, 100, 1), (8, 2, 64, 64, 64, 0),
                                    (3, 1, 32, 64, 1, 5), (2, 1, 128, 128, 300, 17), (4, 4, 16, 24, None, 0),
                                    (16, 1, 64, 128, 130, 3)])
 def test_two_maps_at_the_edges_of_window_and_first_positions(dtype, shape):
@@ -536,7 +536,7 @@ def test_gelu_gate(dtype):
                                                            else dict(rtol=1e-2, atol=1e-2)))
 
 
-@pytest.mark.parametrize("shape", [(4, 1, 48, 96, 96, 4, 16), (8, 2, 32, 64, None, 0, 16), (4, 2, 64, 128, 600, 3, 32),
+@pytest.mark.parametrize("shape", [(5, 1, 48, 80, 90, 6, 16), (8, 2, 32, 64, None, 0, 16), (4, 2, 64, 128, 600, 3, 32),
                                    (32, 1, 16, 16, 50, 2, 8), (2, 2, 80, 48, 1, 0, 16), (6, 2, 64, 128, 300, 300, 64)])
 def test_tensor_core_kernels_against_the_float32_arithmetic(shape):
     """bfloat16 batches of decoding requests (lengths 1, the window's and the kept positions' edges, some with
@@ -588,5 +588,5 @@ def test_decode_splits_fill_the_gpu():
     assert decode_splits(1, 1, 5000, 148) == 16
     assert decode_splits(8, 8, 1028, 148) == 4
     assert decode_splits(64, 8, 4096, 148) == 1          # pairs that fill the GPU by themselves are not split
-    assert tensor_core_sizes_ok(48, 96) and tensor_core_sizes_ok(128, 256)
+    assert tensor_core_sizes_ok(48, 80) and tensor_core_sizes_ok(128, 256)
     assert not tensor_core_sizes_ok(10, 6) and not tensor_core_sizes_ok(64, 512) and not tensor_core_sizes_ok(512, 64)

@@ -77,8 +77,6 @@ def build_spec(config: NodopelConfig) -> ModelSpec:
         if layer.mlp is not None:
             norms["feed_forward"] = _norm(config, "norm2")
             feed_forward = _feed_forward(layer.mlp)
-        elif config.streams is None:
-            raise ValueError("Nodopel without streams: a layer without a feed-forward is not built")
         layers.append(LayerSpec(name=f"l{index}", block=block, mixer=_mixer(config, index), feed_forward=feed_forward,
                                 position=_position(config, index), norms=norms))
     return ModelSpec(

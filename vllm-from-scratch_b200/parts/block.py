@@ -21,12 +21,19 @@ from .base import (BLOCKS, Block, CacheView, FreshStreams, HalfNormedRows, Norm,
 
 @BLOCKS.register("pre_norm")
 class PreNormBlock(Block):
+    """``h += mixer(norm1(h)); h += feed_forward(norm2(h))``; a layer without a feed-forward is its first half."""
+
     norm_roles = ("mixer", "feed_forward")
     graph_safe = True
+    needs_feed_forward = False
+
+    def __init__(self, params, env, *, mixer, feed_forward, norms, side=None) -> None:
+        self.norm_roles = ("mixer", "feed_forward") if feed_forward is not None else ("mixer",)
+        super().__init__(params, env, mixer=mixer, feed_forward=feed_forward, norms=norms, side=side)
 
     def _splits_norms(self, tokens: int) -> bool:
-        return (self.norms["feed_forward"].split() is not None and self.mixer.splits_norms(tokens)
-                and self.feed_forward.splits_norms(tokens))
+        return (self.feed_forward is not None and self.norms["feed_forward"].split() is not None
+                and self.mixer.splits_norms(tokens) and self.feed_forward.splits_norms(tokens))
 
     def first_norm(self) -> Norm:
         return self.norms["mixer"]
@@ -42,6 +49,8 @@ class PreNormBlock(Block):
         normed = x if isinstance(x, HalfNormedRows) else self.norms["mixer"].forward(x, residual)
         if not self._splits_norms(residual.shape[0]):
             mixed = self.mixer.forward(normed, ctx, cache)
+            if self.feed_forward is None:
+                return mixed
             normed = self.norms["feed_forward"].forward(mixed, residual)
             return self.feed_forward.forward(normed, ctx)
         half = self.mixer.forward(normed, ctx, cache, fold=(residual, self.norms["feed_forward"]))
