@@ -579,13 +579,13 @@ def _lobuzen(layers: int, hidden: int, heads: int, inter: int, vocab: int) -> di
 def _nodopel(layers: int, hidden: int, heads: int, inter: int, vocab: int) -> dict:
     """Layers of the sizes of a Qwen3 layer of this width.  The attention has the Qwen3 layer's heads, each as
     two maps of 64 over values of 128 (so the four projections have the Qwen3 layer's shapes), a window of 1024
-    that keeps the first 4 positions, capped scores and stretched frequencies.  The feed-forwards alternate
+    that keeps the first 8 positions, capped scores and stretched frequencies.  The feed-forwards alternate
     between a dense one of the Qwen3 layer's width and a routed one: 2 of 8 experts of a quarter of that width
     and 2 identity experts, beside a shared expert of half the width, so that a token passes through at most as
     many feed-forward parameters as in the Qwen3 layer.  Three streams.  With three layers and more the second
     runs twice in a row, so that ``layers`` counts the runs."""
-    mixer = {"heads": heads, "kv_heads": 8, "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "diff": 0.6, "softcap": 30.0,
-             "mask": {"size": 1024, "keep_first": 4},
+    mixer = {"heads": heads, "kv_heads": 8, "dim": 64, "vdim": 128, "scale": 64 ** -0.5, "diff": 0.5, "softcap": 50.0,
+             "mask": {"size": 1024, "keep_first": 8},
              "rot": {"dims": 64, "base": 1.0e6, "scaling": {"factor": 8.0, "low": 1.0, "high": 4.0, "original": 8192}}}
     dense = {"kind": "dense", "ff": inter}
     moe = {"kind": "moe", "expert": {"ff": inter // 4}, "router": {"experts": 8, "identity": 2, "top": 2},

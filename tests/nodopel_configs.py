@@ -93,7 +93,7 @@ ND_D = {
                rot=_rot(16, 3000.0, (5.0, 1.0, 3.0, 32))),
         _layer(3, 1, 16, 32, 0.25, 0.3, None, window=30, keep=2, rot=_rot(16, 700.0)),
         _layer(2, 1, 32, 48, 0.2, 0.75, _dense(120), window=64, keep=16, rot=_rot(8, 250.0)),
-        _layer(2, 2, 8, 12, 0.4, 0.15, None),
+        _layer(2, 2, 8, 12, 0.4, 0.15, None, window=21),
     ],
 }
 

@@ -537,7 +537,8 @@ def test_gelu_gate(dtype):
 
 
 @pytest.mark.parametrize("shape", [(5, 1, 48, 80, 90, 6, 16), (8, 2, 32, 64, None, 0, 16), (4, 2, 64, 128, 600, 3, 32),
-                                   (32, 1, 16, 16, 50, 2, 8), (2, 2, 80, 48, 1, 0, 16), (6, 2, 64, 128, 300, 300, 64)])
+                                   (32, 1, 16, 16, 50, 2, 8), (2, 2, 80, 48, 1, 0, 16), (6, 2, 64, 128, 300, 300, 64),
+                                   (12, 1, 32, 48, 200, 5, 16), (32, 2, 16, 32, None, 0, 16), (8, 1, 64, 64, 700, 1, 16)])
 def test_tensor_core_kernels_against_the_float32_arithmetic(shape):
     """bfloat16 batches of decoding requests (lengths 1, the window's and the kept positions' edges, some with
     their keys split over several blocks) ahead of portions of prompts (2, 63, 64, 65 and 200 tokens, with and

@@ -13,7 +13,7 @@
 
 static_assert(B200_DIFF_D % 16 == 0 && B200_DIFF_DV % 16 == 0, "sizes must be multiples of 16");
 static_assert(B200_DIFF_DV <= 256, "value heads above 256 would not fit the registers of a thread");
-static_assert(2 * b200::diff_stage_elements<B200_DIFF_D, B200_DIFF_DV>() * 2 <= 220 * 1024 &&
+static_assert(2 * b200::diff_stage_elements<B200_DIFF_D, B200_DIFF_DV>() * 2 + 2 * 64 * 8 <= 220 * 1024 &&
               b200::diff_decode_smem<B200_DIFF_D, B200_DIFF_DV>() <= 220 * 1024, "tiles exceed shared memory");
 
 B200_EXPORT int b200_diff_attention_bf16_sizes(int* d, int* dv) {

@@ -49,25 +49,33 @@ __device__ __forceinline__ KeyList key_list(int first_query, int last_query, int
     return list;
 }
 
-// Entries e0 .. e0 + 63 of the list: key rows [64][2 D + pad] and value rows [64][DV + pad]; entries past
-// the list and pages that were given back are zeros.
-template <int D, int DV>
-__device__ __forceinline__ void load_list_tile(bf16* k_s, bf16* v_s, const bf16* __restrict__ k_pages,
-                                               const bf16* __restrict__ v_pages, const int* __restrict__ table,
-                                               const KeyList& list, int e0, int e_end, int kv_head, int nkv,
-                                               int page_size) {
-    constexpr int kKeyChunks = 2 * D / 8, kValueChunks = DV / 8, kChunks = kKeyChunks + kValueChunks;
-    for (int idx = threadIdx.x; idx < kKeys * kChunks; idx += kDiffThreads) {
-        const int row = idx / kChunks, c = idx - row * kChunks;
-        const int entry = e0 + row;
-        int page = -1, offset = 0;
+// Where the rows of the entries e0 .. e0 + 63 of the list lie in the pages of key/value head `kv_head`, counted in
+// rows: rows[i] for entry e0 + i, -1 for entries past the list and for pages that were given back.  One thread
+// an entry looks its page up, so that the copies that follow divide nothing and wait for no table.
+__device__ __forceinline__ void list_tile_rows(long long* rows, const int* __restrict__ table, const KeyList& list,
+                                               int e0, int e_end, int kv_head, int nkv, int page_size) {
+    if (threadIdx.x < kKeys) {
+        const int entry = e0 + threadIdx.x;
+        long long at = -1;
         if (entry < e_end) {
             const int kp = list.position(entry);
             const int index = kp / page_size;
-            offset = kp - index * page_size;
-            page = table[index];
+            const int page = table[index];
+            if (page >= 0) at = ((long long)page * nkv + kv_head) * page_size + (kp - index * page_size);
         }
-        const size_t at = ((size_t)max(page, 0) * nkv + kv_head) * page_size + offset;
+        rows[threadIdx.x] = at;
+    }
+}
+
+// A tile of 64 entries whose rows `rows` names: key rows [64][2 D + pad] and value rows [64][DV + pad]; zeros
+// where there is no row.
+template <int D, int DV>
+__device__ __forceinline__ void load_list_tile(bf16* k_s, bf16* v_s, const bf16* __restrict__ k_pages,
+                                               const bf16* __restrict__ v_pages, const long long* rows) {
+    constexpr int kKeyChunks = 2 * D / 8, kValueChunks = DV / 8, kChunks = kKeyChunks + kValueChunks;
+    for (int idx = threadIdx.x; idx < kKeys * kChunks; idx += kDiffThreads) {
+        const int row = idx / kChunks, c = idx - row * kChunks;
+        const long long at = rows[row];
         bf16* dst;
         const bf16* src;
         if (c < kKeyChunks) {
@@ -77,7 +85,7 @@ __device__ __forceinline__ void load_list_tile(bf16* k_s, bf16* v_s, const bf16*
             dst = v_s + row * (DV + kDiffPad) + (c - kKeyChunks) * 8;
             src = v_pages + at * DV + (c - kKeyChunks) * 8;
         }
-        if (page >= 0) cp_async16(dst, src);
+        if (at >= 0) cp_async16(dst, src);
         else *reinterpret_cast<uint4*>(dst) = make_uint4(0, 0, 0, 0);
     }
 }
@@ -117,6 +125,41 @@ __device__ __forceinline__ void weighted_values(float (&o)[DV / 8][4], const uns
             mma_bf16(o[2 * (j0 + i)], pa, b[i][0], b[i][1]);
             mma_bf16(o[2 * (j0 + i) + 1], pa, b[i][2], b[i][3]);
         }
+    }
+}
+
+// The same sum for a decode block, transposed: o^T += V^T P^T for 16 entries of a tile.  The 16 x 16 blocks of the
+// value tile are the first operand (16 columns of the head by 16 entries), the weights of eight query heads the
+// second (their score fragments are that operand's fragments as they stand), so that a product's eight columns
+// are eight query heads and none of its rows is padding.  `o[h][j]` holds columns 16 j .. 16 j + 15 of the output
+// of the heads 8 h .. 8 h + 7: elements 0 and 1 the column 16 j + lane / 4 for the heads 8 h + 2 (lane % 4) and the
+// next, elements 2 and 3 the column eight further on.
+template <int DV, int kHalves>
+__device__ __forceinline__ void weighted_values_transposed(float (&o)[kHalves][DV / 16][4], const unsigned (&pa)[4],
+                                                           const unsigned (&pm)[4], const unsigned (&pl)[4],
+                                                           const bf16* v_row) {
+    constexpr int kBlocks = DV / 16, kAtOnce = kBlocks % 4 == 0 ? 4 : kBlocks % 2 == 0 ? 2 : 1;
+#pragma unroll
+    for (int j0 = 0; j0 < kBlocks; j0 += kAtOnce) {
+        unsigned a[kAtOnce][4];
+#pragma unroll
+        for (int i = 0; i < kAtOnce; ++i) {
+            unsigned b[4];
+            ldmatrix_x4_trans(b, v_row + (j0 + i) * 16);
+            a[i][0] = b[0]; a[i][1] = b[2]; a[i][2] = b[1]; a[i][3] = b[3];
+        }
+#pragma unroll
+        for (int i = 0; i < kAtOnce; ++i)
+#pragma unroll
+            for (int h = 0; h < kHalves; ++h) mma_bf16(o[h][j0 + i], a[i], pl[h], pl[2 + h]);
+#pragma unroll
+        for (int i = 0; i < kAtOnce; ++i)
+#pragma unroll
+            for (int h = 0; h < kHalves; ++h) mma_bf16(o[h][j0 + i], a[i], pm[h], pm[2 + h]);
+#pragma unroll
+        for (int i = 0; i < kAtOnce; ++i)
+#pragma unroll
+            for (int h = 0; h < kHalves; ++h) mma_bf16(o[h][j0 + i], a[i], pa[h], pa[2 + h]);
     }
 }
 
@@ -287,19 +330,27 @@ __global__ void __launch_bounds__(kDiffThreads, DV <= 128 ? 2 : 1) diff_prefill_
     auto k_stage = [&](int s) { return stage_base + (size_t)s * kStage; };
     auto v_stage = [&](int s) { return stage_base + (size_t)s * kStage + kKeys * (2 * D + kDiffPad); };
 
-    load_list_tile<D, DV>(k_stage(0), v_stage(0), k_pages, v_pages, table, list, 0, entries, kv_head, p.nkv, p.page_size);
+    // rows_of(i): where the rows of tile i lie, made a turn before the tile's copies start
+    long long* row_slots = reinterpret_cast<long long*>(stage_base + 2 * (size_t)kStage);
+    auto rows_of = [&](int tile) { return row_slots + (tile & 1) * kKeys; };
+    list_tile_rows(rows_of(0), table, list, 0, entries, kv_head, p.nkv, p.page_size);
+    list_tile_rows(rows_of(1), table, list, kKeys, entries, kv_head, p.nkv, p.page_size);
+    __syncthreads();
+    load_list_tile<D, DV>(k_stage(0), v_stage(0), k_pages, v_pages, rows_of(0));
     cp_async_commit();
     for (int t = 0; t < tiles; ++t) {
         const int e0 = t * kKeys;
         if (t + 1 < tiles) {
-            load_list_tile<D, DV>(k_stage((t + 1) & 1), v_stage((t + 1) & 1), k_pages, v_pages, table, list, e0 + kKeys,
-                                  entries, kv_head, p.nkv, p.page_size);
+            load_list_tile<D, DV>(k_stage((t + 1) & 1), v_stage((t + 1) & 1), k_pages, v_pages, rows_of(t + 1));
             cp_async_commit();
             cp_async_wait<1>();
         } else {
             cp_async_wait<0>();
         }
         __syncthreads();
+        // (the copies of tile t were started a turn ago from the slot that the rows of tile t + 2 now take)
+        if (t + 2 < tiles)
+            list_tile_rows(rows_of(t + 2), table, list, e0 + 2 * kKeys, entries, kv_head, p.nkv, p.page_size);
         // A tile wholly behind the kept positions is a run of consecutive positions from k0 on; a warp whose rows
         // all lie before it (causal) or whose windows all lie behind it has nothing to add.
         const bool plain_run = e0 >= list.kept;
@@ -352,7 +403,7 @@ template <int D, int DV>
 int launch_diff_prefill_mma(const void* q, const void* k_pages, const void* v_pages, void* out, const DiffMmaArgs& p,
                             int num_tokens, cudaStream_t stream) {
     auto kernel = diff_prefill_mma_kernel<D, DV>;
-    const int stages = 2 * diff_stage_elements<D, DV>() * (int)sizeof(bf16);
+    const int stages = 2 * diff_stage_elements<D, DV>() * (int)sizeof(bf16) + 2 * kKeys * (int)sizeof(long long);
     const int exchange = 64 * (DV + 8) * (int)sizeof(float);
     const int smem = stages > exchange ? stages : exchange;
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -368,8 +419,10 @@ int launch_diff_prefill_mma(const void* q, const void* k_pages, const void* v_pa
 // belong to each map, and each takes 16 of a tile's 64 entries; the warps of a map merge through shared memory,
 // and with one split the block also forms the difference and its norm.  With several splits the merged
 // (maximum, sum, output) of each map go to scratch: partial_o [(head * 2 + map) * splits + split][DV],
-// partial_ml the same rows of [2].
-template <int D, int DV>
+// partial_ml the same rows of [2].  The product with the values is the transposed one (weighted_values_transposed),
+// over the first eight heads of the fragment (kHalves 1: up to eight query heads to a key/value head; the scores
+// of the other eight rows are not even capped) or over both halves (kHalves 2).
+template <int D, int DV, int kHalves>
 __global__ void __launch_bounds__(kDiffThreads) diff_decode_mma_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
     bf16* __restrict__ out, float* __restrict__ partial_o, float* __restrict__ partial_ml, const DiffMmaArgs p,
@@ -400,21 +453,30 @@ __global__ void __launch_bounds__(kDiffThreads) diff_decode_mma_kernel(
     load_q_fragments<D>(qa, row_a < group ? q_base + (size_t)row_a * 2 * D : nullptr,
                         row_b < group ? q_base + (size_t)row_b * 2 * D : nullptr, lane);
 
-    float o[DV / 8][4];
+    float o[kHalves][DV / 16][4];
 #pragma unroll
-    for (int i = 0; i < DV / 8; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.0f;
+    for (int h = 0; h < kHalves; ++h)
+#pragma unroll
+        for (int i = 0; i < DV / 16; ++i) o[h][i][0] = o[h][i][1] = o[h][i][2] = o[h][i][3] = 0.0f;
     float m_a = -INFINITY, m_b = -INFINITY, l_a = 0.0f, l_b = 0.0f;
+    // the heads of this lane's columns of the transposed output sit in the lanes 4 * head as rows of the scores
+    const int column_lane = (lane & 3) * 8;
 
     auto k_stage = [&](int s) { return stage_base + (size_t)s * kStage; };
     auto v_stage = [&](int s) { return stage_base + (size_t)s * kStage + kKeys * (2 * D + kDiffPad); };
 
     // A decode block waits for memory and little else: two tiles are on their way while one is used (a group of
     // copies is committed every turn, an empty one too, so that the count behind the wait is the same every turn).
+    // Where the rows of tile i lie is looked up a turn before the tile's copies start (slot i % stages).
+    long long* row_slots = reinterpret_cast<long long*>(stage_base + kDiffDecodeStages * (size_t)kStage);
+    auto rows_of = [&](int tile) { return row_slots + (tile % kDiffDecodeStages) * kKeys; };
+#pragma unroll
+    for (int s = 0; s < kDiffDecodeStages; ++s)
+        list_tile_rows(rows_of(s), table, list, my_begin + s * kKeys, my_end, kv_head, p.nkv, p.page_size);
+    __syncthreads();
 #pragma unroll
     for (int s = 0; s < kDiffDecodeStages - 1; ++s) {
-        if (s < tiles)
-            load_list_tile<D, DV>(k_stage(s), v_stage(s), k_pages, v_pages, table, list, my_begin + s * kKeys, my_end,
-                                  kv_head, p.nkv, p.page_size);
+        if (s < tiles) load_list_tile<D, DV>(k_stage(s), v_stage(s), k_pages, v_pages, rows_of(s));
         cp_async_commit();
     }
     const int mi = lane >> 3, ri = lane & 7;
@@ -423,10 +485,14 @@ __global__ void __launch_bounds__(kDiffThreads) diff_decode_mma_kernel(
         const int ahead = t + kDiffDecodeStages - 1;
         if (ahead < tiles)
             load_list_tile<D, DV>(k_stage(ahead % kDiffDecodeStages), v_stage(ahead % kDiffDecodeStages), k_pages, v_pages,
-                                  table, list, my_begin + ahead * kKeys, my_end, kv_head, p.nkv, p.page_size);
+                                  rows_of(ahead));
         cp_async_commit();
         cp_async_wait<kDiffDecodeStages - 1>();
         __syncthreads();
+        // the slot of tile t is free (its copies were started two turns ago): the rows of tile t + stages
+        if (t + kDiffDecodeStages < tiles)
+            list_tile_rows(rows_of(t + kDiffDecodeStages), table, list, e0 + kDiffDecodeStages * kKeys, my_end, kv_head,
+                           p.nkv, p.page_size);
         const bf16* k_map = k_stage(t % kDiffDecodeStages) + map * D;
         const bf16* v_s = v_stage(t % kDiffDecodeStages);
 
@@ -443,7 +509,7 @@ __global__ void __launch_bounds__(kDiffThreads) diff_decode_mma_kernel(
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt)
 #pragma unroll
-            for (int e = 0; e < 4; ++e) {
+            for (int e = 0; e < 2 * kHalves; ++e) {
                 const int entry = e0 + part * 16 + nt * 8 + (lane & 3) * 2 + (e & 1);
                 float v = capped_log2(s[nt][e] * p.scale, p.softcap, inv_cap);
                 if (entry >= my_end) v = -INFINITY;       // every entry of the list is visible to the one query
@@ -451,34 +517,57 @@ __global__ void __launch_bounds__(kDiffThreads) diff_decode_mma_kernel(
                 if (e < 2) max_a = fmaxf(max_a, v); else max_b = fmaxf(max_b, v);
             }
         max_a = quad_max(max_a);
-        max_b = quad_max(max_b);
-        const float new_a = fmaxf(m_a, max_a), new_b = fmaxf(m_b, max_b);
-        const float ref_a = new_a == -INFINITY ? 0.0f : new_a, ref_b = new_b == -INFINITY ? 0.0f : new_b;
-        const float alpha_a = exp2f(m_a - ref_a), alpha_b = exp2f(m_b - ref_b);
+        const float new_a = fmaxf(m_a, max_a);
+        const float ref_a = new_a == -INFINITY ? 0.0f : new_a;
+        const float alpha_a = exp2f(m_a - ref_a);
         m_a = new_a;
-        m_b = new_b;
-        float sum_a = 0.0f, sum_b = 0.0f;
+        float sum_a = 0.0f;
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
             s[nt][0] = exp2f(s[nt][0] - ref_a);
             s[nt][1] = exp2f(s[nt][1] - ref_a);
-            s[nt][2] = exp2f(s[nt][2] - ref_b);
-            s[nt][3] = exp2f(s[nt][3] - ref_b);
             sum_a += s[nt][0] + s[nt][1];
-            sum_b += s[nt][2] + s[nt][3];
         }
         l_a = l_a * alpha_a + sum_a;
-        l_b = l_b * alpha_b + sum_b;
+        float alpha_b = 1.0f;
+        if constexpr (kHalves == 2) {
+            max_b = quad_max(max_b);
+            const float new_b = fmaxf(m_b, max_b);
+            const float ref_b = new_b == -INFINITY ? 0.0f : new_b;
+            alpha_b = exp2f(m_b - ref_b);
+            m_b = new_b;
+            float sum_b = 0.0f;
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt) {
+                s[nt][2] = exp2f(s[nt][2] - ref_b);
+                s[nt][3] = exp2f(s[nt][3] - ref_b);
+                sum_b += s[nt][2] + s[nt][3];
+            }
+            l_b = l_b * alpha_b + sum_b;
+        } else {
+            s[0][2] = s[0][3] = s[1][2] = s[1][3] = 0.0f;
+        }
         unsigned pa[4], pm[4], pl[4];
         split_bf16x3(s[0][0], s[0][1], pa[0], pm[0], pl[0]);
-        split_bf16x3(s[0][2], s[0][3], pa[1], pm[1], pl[1]);
         split_bf16x3(s[1][0], s[1][1], pa[2], pm[2], pl[2]);
-        split_bf16x3(s[1][2], s[1][3], pa[3], pm[3], pl[3]);
-#pragma unroll
-        for (int nt = 0; nt < DV / 8; ++nt) {
-            o[nt][0] *= alpha_a; o[nt][1] *= alpha_a; o[nt][2] *= alpha_b; o[nt][3] *= alpha_b;
+        if constexpr (kHalves == 2) {
+            split_bf16x3(s[0][2], s[0][3], pa[1], pm[1], pl[1]);
+            split_bf16x3(s[1][2], s[1][3], pa[3], pm[3], pl[3]);
+        } else {
+            pa[1] = pm[1] = pl[1] = pa[3] = pm[3] = pl[3] = 0u;
         }
-        weighted_values<DV>(o, pa, pm, pl, v_s + (part * 16 + (mi & 1) * 8 + ri) * (DV + kDiffPad) + (mi >> 1) * 8);
+#pragma unroll
+        for (int h = 0; h < kHalves; ++h) {
+            const float alpha = h == 0 ? alpha_a : alpha_b;
+            const float even = __shfl_sync(0xffffffffu, alpha, column_lane);
+            const float odd = __shfl_sync(0xffffffffu, alpha, column_lane + 4);
+#pragma unroll
+            for (int j = 0; j < DV / 16; ++j) {
+                o[h][j][0] *= even; o[h][j][1] *= odd; o[h][j][2] *= even; o[h][j][3] *= odd;
+            }
+        }
+        weighted_values_transposed<DV, kHalves>(o, pa, pm, pl,
+                                                v_s + (part * 16 + (mi & 1) * 8 + ri) * (DV + kDiffPad) + (mi >> 1) * 8);
         __syncthreads();
     }
 
@@ -489,14 +578,20 @@ __global__ void __launch_bounds__(kDiffThreads) diff_decode_mma_kernel(
     float* red_ml = red_o + 8 * 16 * DV;                          // [8 warps][16][2]
     float* merged = red_ml + 8 * 16 * 2;                          // [2 maps][16][DV], normalised
 #pragma unroll
-    for (int nt = 0; nt < DV / 8; ++nt) {
-        const int col = nt * 8 + (lane & 3) * 2;
-        *reinterpret_cast<float2*>(red_o + ((size_t)warp * 16 + row_a) * DV + col) = make_float2(o[nt][0], o[nt][1]);
-        *reinterpret_cast<float2*>(red_o + ((size_t)warp * 16 + row_b) * DV + col) = make_float2(o[nt][2], o[nt][3]);
-    }
+    for (int h = 0; h < kHalves; ++h)
+#pragma unroll
+        for (int j = 0; j < DV / 16; ++j) {
+            float* at = red_o + ((size_t)warp * 16 + h * 8 + (lane & 3) * 2) * DV + j * 16 + (lane >> 2);
+            at[0] = o[h][j][0];
+            at[DV] = o[h][j][1];
+            at[8] = o[h][j][2];
+            at[DV + 8] = o[h][j][3];
+        }
     if ((lane & 3) == 0) {
         red_ml[(warp * 16 + row_a) * 2] = m_a; red_ml[(warp * 16 + row_a) * 2 + 1] = l_a;
-        red_ml[(warp * 16 + row_b) * 2] = m_b; red_ml[(warp * 16 + row_b) * 2 + 1] = l_b;
+        if constexpr (kHalves == 2) {
+            red_ml[(warp * 16 + row_b) * 2] = m_b; red_ml[(warp * 16 + row_b) * 2 + 1] = l_b;
+        }
     }
     __syncthreads();
     for (int idx = tid; idx < 2 * group * DV; idx += kDiffThreads) {
@@ -589,7 +684,8 @@ __global__ void __launch_bounds__(128) diff_merge_splits_kernel(
 
 template <int D, int DV>
 constexpr int diff_decode_smem() {
-    constexpr int stages = kDiffDecodeStages * diff_stage_elements<D, DV>() * (int)sizeof(bf16);
+    constexpr int stages = kDiffDecodeStages * diff_stage_elements<D, DV>() * (int)sizeof(bf16) +
+                           kDiffDecodeStages * kKeys * (int)sizeof(long long);
     constexpr int merge = (8 * 16 * DV + 8 * 16 * 2 + 2 * 16 * DV) * (int)sizeof(float);
     return stages > merge ? stages : merge;
 }
@@ -597,7 +693,8 @@ constexpr int diff_decode_smem() {
 template <int D, int DV>
 int launch_diff_decode_mma(const void* q, const void* k_pages, const void* v_pages, void* out, float* partial_o,
                            float* partial_ml, const DiffMmaArgs& p, int splits, cudaStream_t stream) {
-    auto kernel = diff_decode_mma_kernel<D, DV>;
+    // up to eight query heads to a key/value head fill one half of a fragment's rows
+    auto kernel = p.nq / p.nkv > 8 ? diff_decode_mma_kernel<D, DV, 2> : diff_decode_mma_kernel<D, DV, 1>;
     constexpr int smem = diff_decode_smem<D, DV>();
     cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (status != cudaSuccess) return fail("diff_decode_attention", cudaGetErrorString(status));

@@ -34,7 +34,7 @@ def tensor_core_sizes_ok(head_dim: int, value_dim: int) -> bool:
     of 64 keys and values, as well as its room for its warps' partial results, within a block's shared memory."""
     if head_dim % 16 or value_dim % 16 or head_dim <= 0 or not 0 < value_dim <= 256:
         return False
-    stages = 3 * 64 * ((MAPS * head_dim + 8) + (value_dim + 8)) * 2
+    stages = 3 * 64 * ((MAPS * head_dim + 8) + (value_dim + 8)) * 2 + 3 * 64 * 8     # and where each entry's row lies
     merge = (8 * 16 * value_dim + 8 * 16 * 2 + 2 * 16 * value_dim) * 4
     return max(stages, merge) <= SHARED_MEMORY_LIMIT
 
