@@ -249,7 +249,7 @@ def rounded(tensor, dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("shape", [(1, 64), (2, 50), (3, 320), (5, 37), (8, 1024)])
+@pytest.mark.parametrize("shape", [(1, 64), (2, 50), (3, 352), (5, 37), (8, 1024), (11, 72), (16, 128)])
 def test_streams_between_two_sublayers(dtype, shape):
     """Every stream set to the embedding's rows; the update by a sublayer's rows with the read and norm of the
     next; the plain sum for the last norm, on a few rows only and without touching the streams."""
@@ -293,7 +293,8 @@ def test_streams_between_two_sublayers(dtype, shape):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("shape", [(5, 1, 48, 80, 32), (3, 3, 10, 6, 6), (2, 1, 64, 128, 0), (6, 2, 16, 24, 16), (1, 1, 128, 64, 2)])
+@pytest.mark.parametrize("shape", [(5, 1, 48, 80, 32), (3, 3, 10, 6, 6), (2, 1, 64, 128, 0), (6, 2, 16, 24, 16), (1, 1, 128, 64, 2),
+                                   (2, 2, 20, 12, 8), (2, 1, 6, 10, 4), (3, 1, 32, 16, 32)])
 def test_bias_rotation_and_pages(dtype, shape):
     """Biases, the rotation of the first numbers of every map of every head at far positions, keys and
     values into scattered slots; a token without a slot stores nothing."""

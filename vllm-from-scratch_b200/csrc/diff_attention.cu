@@ -20,67 +20,108 @@
 
 namespace b200 {
 
-// A block is one token and `units_per_block` of its units (a unit: one map of a query or key head, or a value
-// head), a warp per unit in turn.  The token's cosines and sines are formed once a block, in shared memory.
-template <typename T>
+// W numbers of a row that are loaded and stored as one (16 bytes at most).
+template <typename T, int W>
+struct alignas(sizeof(T) * W) RowPiece { T v[W]; };
+
+// A block is one token and `pieces_per_block` pieces of W numbers of its row, a thread a piece in turn: every
+// piece of the output is made by one thread, which for a rotated piece also reads the piece half the rotated
+// numbers away.  The token's cosines and sines are formed once a block, in shared memory.  W divides the map
+// size, half the rotated numbers and the value size, and every row starts on a multiple of W numbers.
+template <typename T, int W>
 __global__ void bias_rope_cache_kernel(const T* __restrict__ qkv, const float* __restrict__ bias,
                                        const int* __restrict__ positions, const int* __restrict__ slots,
                                        const float* __restrict__ inv_freq, T* __restrict__ q_out,
                                        T* __restrict__ k_pages, T* __restrict__ v_pages, int q_units, int k_units,
                                        int v_heads, int maps, int d, int dv, int rotary_dim, int page_size,
-                                       int units_per_block) {
+                                       int pieces_per_block) {
     extern __shared__ float turn[];                 // [rotary_dim / 2] cosines, then as many sines
+    using Piece = RowPiece<T, W>;
     overlap_trigger();
     overlap_wait();
     const int token = blockIdx.x;
-    const int warps = blockDim.x >> 5;
-    const int lane = threadIdx.x & 31;
     const int half = rotary_dim >> 1;
     const float position = (float)positions[token];
     for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(position * inv_freq[j], &turn[half + j], &turn[j]);
     __syncthreads();
-    const int units = q_units + k_units + v_heads;
-    const int first = blockIdx.y * units_per_block, last = min(units, first + units_per_block);
-    const size_t width = (size_t)(q_units + k_units) * d + (size_t)v_heads * dv;
+    const int qk_width = (q_units + k_units) * d, width = qk_width + v_heads * dv;
+    const int first = blockIdx.y * pieces_per_block, last = min(width / W, first + pieces_per_block);
     const T* row = qkv + (size_t)token * width;
     const int slot = k_pages != nullptr ? slots[token] : -1;
     const int page = slot >= 0 ? slot / page_size : 0, offset = slot >= 0 ? slot - page * page_size : 0;
-    for (int unit = first + (threadIdx.x >> 5); unit < last; unit += warps) {
-        const bool is_q = unit < q_units;
-        if (!is_q && slot < 0) continue;
-        if (unit >= q_units + k_units) {
-            const int head = unit - q_units - k_units;
-            const size_t column = (size_t)(q_units + k_units) * d + (size_t)head * dv;
-            T* dst = v_pages + (((size_t)page * v_heads + head) * page_size + offset) * dv;
-            for (int j = lane; j < dv; j += 32) {
-                float v = to_float(row[column + j]);
-                if (bias) v += bias[column + j];
-                dst[j] = from_float<T>(v);
-            }
-            continue;
-        }
-        const size_t column = (size_t)unit * d;
+    const int q_width = q_units * d, k_heads = k_units / maps;
+    for (int piece = first + threadIdx.x; piece < last; piece += blockDim.x) {
+        const int column = piece * W;
+        if (column >= q_width && slot < 0) continue;
+        const Piece in = *reinterpret_cast<const Piece*>(row + column);
+        float x[W];
+#pragma unroll
+        for (int w = 0; w < W; ++w) x[w] = to_float(in.v[w]) + (bias ? bias[column + w] : 0.0f);
         T* dst;
-        if (is_q) {
-            dst = q_out + (size_t)token * q_units * d + column;
+        if (column >= qk_width) {
+            const int head = (column - qk_width) / dv, j = column - qk_width - head * dv;
+            dst = v_pages + (((size_t)page * v_heads + head) * page_size + offset) * dv + j;
         } else {
-            const int ku = unit - q_units, heads = k_units / maps;
-            dst = k_pages + ((((size_t)page * heads + ku / maps) * page_size + offset) * maps + ku % maps) * d;
+            const int unit = column / d, j = column - unit * d;
+            if (column < q_width) {
+                dst = q_out + (size_t)token * q_width + column;
+            } else {
+                const int ku = unit - q_units;
+                dst = k_pages + ((((size_t)page * k_heads + ku / maps) * page_size + offset) * maps + ku % maps) * d + j;
+            }
+            if (j < rotary_dim) {
+                // the pair (i, i + half): this piece holds the first numbers of its pairs or the second
+                const bool lower = j < half;
+                const int other = lower ? column + half : column - half, at = lower ? j : j - half;
+                const Piece partner = *reinterpret_cast<const Piece*>(row + other);
+#pragma unroll
+                for (int w = 0; w < W; ++w) {
+                    const float y = to_float(partner.v[w]) + (bias ? bias[other + w] : 0.0f);
+                    float o1, o2;
+                    if (lower) rotate_pair(x[w], y, turn[at + w], turn[half + at + w], o1, o2);
+                    else rotate_pair(y, x[w], turn[at + w], turn[half + at + w], o1, o2);
+                    x[w] = lower ? o1 : o2;
+                }
+            }
         }
-        for (int j = lane; j < half; j += 32) {
-            float u = to_float(row[column + j]), v = to_float(row[column + j + half]);
-            if (bias) { u += bias[column + j]; v += bias[column + j + half]; }
-            float o1, o2;
-            rotate_pair(u, v, turn[j], turn[half + j], o1, o2);
-            dst[j] = from_float<T>(o1);
-            dst[j + half] = from_float<T>(o2);
-        }
-        for (int j = rotary_dim + lane; j < d; j += 32) {
-            float v = to_float(row[column + j]);
-            if (bias) v += bias[column + j];
-            dst[j] = from_float<T>(v);
-        }
+        Piece made;
+#pragma unroll
+        for (int w = 0; w < W; ++w) made.v[w] = from_float<T>(x[w]);
+        *reinterpret_cast<Piece*>(dst) = made;
     }
+}
+
+template <typename T, int W>
+void launch_bias_rope_cache(const void* qkv, const float* bias, const int* positions, const int* slots,
+                            const float* inv_freq, void* q_out, void* k_pages, void* v_pages, int num_tokens,
+                            int q_units, int k_units, int v_heads, int maps, int d, int dv, int rotary_dim,
+                            int page_size, cudaStream_t stream) {
+    // Many tokens: a block takes all of a token's row, so that its cosines and sines are formed once; few tokens:
+    // a piece to a thread, so that the launch has blocks enough.
+    const int threads = 256;
+    const int pieces = ((q_units + k_units) * d + v_heads * dv) / W;
+    const int pieces_per_block = num_tokens >= 256 ? pieces : threads;
+    dim3 grid(num_tokens, (pieces + pieces_per_block - 1) / pieces_per_block);
+    const size_t smem = sizeof(float) * (size_t)rotary_dim;
+    launch_overlapped_if(num_tokens <= kOverlapMostRows, bias_rope_cache_kernel<T, W>, grid, threads, smem, stream,
+                         (const T*)qkv, bias, positions, slots, inv_freq, (T*)q_out, (T*)k_pages, (T*)v_pages, q_units,
+                         k_units, v_heads, maps, d, dv, rotary_dim, page_size, pieces_per_block);
+}
+
+template <typename T>
+void dispatch_bias_rope_cache(int pieces_of, const void* qkv, const float* bias, const int* positions, const int* slots,
+                              const float* inv_freq, void* q_out, void* k_pages, void* v_pages, int num_tokens,
+                              int q_units, int k_units, int v_heads, int maps, int d, int dv, int rotary_dim,
+                              int page_size, cudaStream_t stream) {
+#define B200_CASE(W)                                                                                                  \
+    if (pieces_of == W)                                                                                               \
+        return launch_bias_rope_cache<T, W>(qkv, bias, positions, slots, inv_freq, q_out, k_pages, v_pages, num_tokens, \
+                                            q_units, k_units, v_heads, maps, d, dv, rotary_dim, page_size, stream);
+    if constexpr (sizeof(T) == 2) { B200_CASE(8) }
+    B200_CASE(4) B200_CASE(2)
+#undef B200_CASE
+    launch_bias_rope_cache<T, 1>(qkv, bias, positions, slots, inv_freq, q_out, k_pages, v_pages, num_tokens, q_units,
+                                 k_units, v_heads, maps, d, dv, rotary_dim, page_size, stream);
 }
 
 constexpr int kQueryTile = 16;
@@ -298,24 +339,22 @@ B200_EXPORT int b200_bias_rope_cache(const void* qkv, const float* bias, const i
     if ((k_pages == nullptr) != (v_pages == nullptr)) return fail("bias_rope_cache", "key and value pages must be given together");
     if (k_pages && page_size <= 0) return fail("bias_rope_cache", "page_size must be positive");
     const int k_units = v_heads * maps;
-    const int units = q_units + k_units + v_heads;
-    // Many tokens: a block takes all of a token's units, so that its cosines and sines are formed once; few tokens:
-    // a unit to a warp, so that the launch has blocks enough.
-    const int warps = 8;
-    const int units_per_block = num_tokens >= 256 ? units : warps;
-    dim3 grid(num_tokens, (units + units_per_block - 1) / units_per_block);
-    if (grid.y > 65535) return fail("bias_rope_cache", "too many heads");
-    const size_t smem = sizeof(float) * (size_t)rotary_dim;
+    if (((size_t)q_units + k_units) * d + (size_t)v_heads * dv > 2147483647u) return fail("bias_rope_cache", "a row is too wide");
+    if (dtype != 0 && dtype != 1) return fail("bias_rope_cache", "dtype must be 0 (float32) or 1 (bfloat16)");
+    // The widest pieces (16 bytes at most) that the sizes and the addresses allow.
+    const int size = dtype == 0 ? 4 : 2;
+    const uintptr_t all = (uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages;
+    int pieces_of = 16 / size;
+    while (pieces_of > 1 && (d % pieces_of || dv % pieces_of || (rotary_dim / 2) % pieces_of ||
+                             (all % (uintptr_t)(pieces_of * size)) != 0))
+        pieces_of >>= 1;
     if (dtype == 0)
-        launch_overlapped_if(num_tokens <= kOverlapMostRows, bias_rope_cache_kernel<float>, grid, warps * 32, smem, stream,
-            (const float*)qkv, bias, positions, slots, inv_freq, (float*)q_out, (float*)k_pages, (float*)v_pages,
-            q_units, k_units, v_heads, maps, d, dv, rotary_dim, page_size, units_per_block);
-    else if (dtype == 1)
-        launch_overlapped_if(num_tokens <= kOverlapMostRows, bias_rope_cache_kernel<__nv_bfloat16>, grid, warps * 32, smem, stream,
-            (const __nv_bfloat16*)qkv, bias, positions, slots, inv_freq, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pages,
-            (__nv_bfloat16*)v_pages, q_units, k_units, v_heads, maps, d, dv, rotary_dim, page_size, units_per_block);
+        dispatch_bias_rope_cache<float>(pieces_of, qkv, bias, positions, slots, inv_freq, q_out, k_pages, v_pages,
+                                        num_tokens, q_units, k_units, v_heads, maps, d, dv, rotary_dim, page_size, stream);
     else
-        return fail("bias_rope_cache", "dtype must be 0 (float32) or 1 (bfloat16)");
+        dispatch_bias_rope_cache<__nv_bfloat16>(pieces_of, qkv, bias, positions, slots, inv_freq, q_out, k_pages, v_pages,
+                                                num_tokens, q_units, k_units, v_heads, maps, d, dv, rotary_dim, page_size,
+                                                stream);
     return check_launch("bias_rope_cache");
 }
 

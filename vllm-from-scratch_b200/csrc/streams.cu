@@ -16,7 +16,7 @@
 
 namespace b200 {
 
-constexpr int kMaxStreams = 8;
+constexpr int kMaxStreams = 16;
 
 __device__ __forceinline__ float4 four_of(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ float4 four_of(const __nv_bfloat16* p) {
@@ -45,7 +45,7 @@ __global__ void stream_mix_norm_kernel(const T* __restrict__ y, const float* __r
     extern __shared__ float u_s[];                      // [H] the row that the sublayer ahead reads
     __shared__ float c_mix[kMaxStreams * kMaxStreams], c_out[kMaxStreams], c_in[kMaxStreams], scratch[33];
     // the small tables are weights: no kernel of the step writes them
-    if (threadIdx.x < S * S) c_mix[threadIdx.x] = mix ? mix[threadIdx.x] : 0.0f;
+    for (int i = threadIdx.x; i < S * S; i += blockDim.x) c_mix[i] = mix ? mix[i] : 0.0f;
     if (threadIdx.x < S) {
         c_out[threadIdx.x] = out_w ? out_w[threadIdx.x] : 0.0f;
         c_in[threadIdx.x] = in_w ? in_w[threadIdx.x] : 1.0f;
@@ -144,8 +144,9 @@ int launch_streams_v(const void* y, const float* fresh, const float* mix, const 
                      const float* in_w, const float* norm_w, float eps, void* normed, const int* rows, int out_rows,
                      int H, cudaStream_t stream) {
     const uintptr_t all = (uintptr_t)y | (uintptr_t)fresh | (uintptr_t)streams | (uintptr_t)norm_w | (uintptr_t)normed;
-    if (H % 4 == 0 && (all & 15) == 0)
-        return launch_streams<T, S, 4>(y, fresh, mix, out_w, streams, in_w, norm_w, eps, normed, rows, out_rows, H, stream);
+    if constexpr (S <= 8)               // four columns of more streams than that would not stay in registers
+        if (H % 4 == 0 && (all & 15) == 0)
+            return launch_streams<T, S, 4>(y, fresh, mix, out_w, streams, in_w, norm_w, eps, normed, rows, out_rows, H, stream);
     return launch_streams<T, S, 1>(y, fresh, mix, out_w, streams, in_w, norm_w, eps, normed, rows, out_rows, H, stream);
 }
 
@@ -157,8 +158,9 @@ int dispatch_streams(int S, const void* y, const float* fresh, const float* mix,
     if (S == N)                                                                                                     \
         return launch_streams_v<T, N>(y, fresh, mix, out_w, streams, in_w, norm_w, eps, normed, rows, out_rows, H, stream);
     B200_CASE(1) B200_CASE(2) B200_CASE(3) B200_CASE(4) B200_CASE(5) B200_CASE(6) B200_CASE(7) B200_CASE(8)
+    B200_CASE(9) B200_CASE(10) B200_CASE(11) B200_CASE(12) B200_CASE(13) B200_CASE(14) B200_CASE(15) B200_CASE(16)
 #undef B200_CASE
-    return fail("stream_mix_norm", "more than 8 streams are not built");
+    return fail("stream_mix_norm", "more than 16 streams are not built");
 }
 
 }  // namespace b200

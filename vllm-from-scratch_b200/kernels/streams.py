@@ -10,7 +10,7 @@ import torch
 from . import _F, _I, _P, KernelError, _check, _code, _run, _stream
 
 _RUN = (torch.float32, torch.bfloat16)
-MAX_STREAMS = 8
+MAX_STREAMS = 16
 
 
 def stream_mix_norm(streams: torch.Tensor, *, rows_in: torch.Tensor | None = None, mix: torch.Tensor | None = None,
