@@ -24,17 +24,18 @@ namespace b200 {
 template <typename T, int W>
 struct alignas(sizeof(T) * W) RowPiece { T v[W]; };
 
-// A block is one token and `pieces_per_block` pieces of W numbers of its row, a thread a piece in turn: every
-// piece of the output is made by one thread, which for a rotated piece also reads the piece half the rotated
-// numbers away.  The token's cosines and sines are formed once a block, in shared memory.  W divides the map
-// size, half the rotated numbers and the value size, and every row starts on a multiple of W numbers.
+// A block is one token and `items_per_block` items of its row, a thread an item in turn.  An item is a piece of W
+// numbers: of a value head, of the numbers of a map that are not rotated, or, where the map is rotated, the pieces
+// of the first and of the second numbers of W pairs (i, i + half) together, so that a map has (d - half) / W items
+// and every number is read once.  The token's cosines and sines are formed once a block, in shared memory.  W
+// divides the map size, half the rotated numbers and the value size, and every row starts on a multiple of W.
 template <typename T, int W>
 __global__ void bias_rope_cache_kernel(const T* __restrict__ qkv, const float* __restrict__ bias,
                                        const int* __restrict__ positions, const int* __restrict__ slots,
                                        const float* __restrict__ inv_freq, T* __restrict__ q_out,
                                        T* __restrict__ k_pages, T* __restrict__ v_pages, int q_units, int k_units,
                                        int v_heads, int maps, int d, int dv, int rotary_dim, int page_size,
-                                       int pieces_per_block) {
+                                       int items_per_block) {
     extern __shared__ float turn[];                 // [rotary_dim / 2] cosines, then as many sines
     using Piece = RowPiece<T, W>;
     overlap_trigger();
@@ -45,48 +46,55 @@ __global__ void bias_rope_cache_kernel(const T* __restrict__ qkv, const float* _
     for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(position * inv_freq[j], &turn[half + j], &turn[j]);
     __syncthreads();
     const int qk_width = (q_units + k_units) * d, width = qk_width + v_heads * dv;
-    const int first = blockIdx.y * pieces_per_block, last = min(width / W, first + pieces_per_block);
+    const int per_map = (d - half) / W, map_items = (q_units + k_units) * per_map;
+    const int items = map_items + v_heads * dv / W;
+    const int first = blockIdx.y * items_per_block, last = min(items, first + items_per_block);
     const T* row = qkv + (size_t)token * width;
     const int slot = k_pages != nullptr ? slots[token] : -1;
     const int page = slot >= 0 ? slot / page_size : 0, offset = slot >= 0 ? slot - page * page_size : 0;
-    const int q_width = q_units * d, k_heads = k_units / maps;
-    for (int piece = first + threadIdx.x; piece < last; piece += blockDim.x) {
-        const int column = piece * W;
-        if (column >= q_width && slot < 0) continue;
+    const int k_heads = k_units / maps;
+    for (int item = first + threadIdx.x; item < last; item += blockDim.x) {
+        int column, j = 0, unit = 0;
+        if (item >= map_items) {
+            column = qk_width + (item - map_items) * W;
+        } else {
+            unit = item / per_map;
+            j = (item - unit * per_map) * W;
+            if (j >= half) j += half;                   // behind the pairs: the numbers that are not rotated
+            column = unit * d + j;
+        }
+        if (column >= q_units * d && slot < 0) continue;
+        T* dst;
+        if (column >= qk_width) {
+            const int head = (column - qk_width) / dv;
+            dst = v_pages + (((size_t)page * v_heads + head) * page_size + offset) * dv + (column - qk_width - head * dv);
+        } else if (unit < q_units) {
+            dst = q_out + (size_t)token * q_units * d + column;
+        } else {
+            const int ku = unit - q_units;
+            dst = k_pages + ((((size_t)page * k_heads + ku / maps) * page_size + offset) * maps + ku % maps) * d + j;
+        }
         const Piece in = *reinterpret_cast<const Piece*>(row + column);
         float x[W];
 #pragma unroll
         for (int w = 0; w < W; ++w) x[w] = to_float(in.v[w]) + (bias ? bias[column + w] : 0.0f);
-        T* dst;
-        if (column >= qk_width) {
-            const int head = (column - qk_width) / dv, j = column - qk_width - head * dv;
-            dst = v_pages + (((size_t)page * v_heads + head) * page_size + offset) * dv + j;
-        } else {
-            const int unit = column / d, j = column - unit * d;
-            if (column < q_width) {
-                dst = q_out + (size_t)token * q_width + column;
-            } else {
-                const int ku = unit - q_units;
-                dst = k_pages + ((((size_t)page * k_heads + ku / maps) * page_size + offset) * maps + ku % maps) * d + j;
-            }
-            if (j < rotary_dim) {
-                // the pair (i, i + half): this piece holds the first numbers of its pairs or the second
-                const bool lower = j < half;
-                const int other = lower ? column + half : column - half, at = lower ? j : j - half;
-                const Piece partner = *reinterpret_cast<const Piece*>(row + other);
-#pragma unroll
-                for (int w = 0; w < W; ++w) {
-                    const float y = to_float(partner.v[w]) + (bias ? bias[other + w] : 0.0f);
-                    float o1, o2;
-                    if (lower) rotate_pair(x[w], y, turn[at + w], turn[half + at + w], o1, o2);
-                    else rotate_pair(y, x[w], turn[at + w], turn[half + at + w], o1, o2);
-                    x[w] = lower ? o1 : o2;
-                }
-            }
-        }
         Piece made;
+        if (column < qk_width && j < half) {
+            const Piece second = *reinterpret_cast<const Piece*>(row + column + half);
+            Piece turned;
 #pragma unroll
-        for (int w = 0; w < W; ++w) made.v[w] = from_float<T>(x[w]);
+            for (int w = 0; w < W; ++w) {
+                const float y = to_float(second.v[w]) + (bias ? bias[column + half + w] : 0.0f);
+                float o1, o2;
+                rotate_pair(x[w], y, turn[j + w], turn[half + j + w], o1, o2);
+                made.v[w] = from_float<T>(o1);
+                turned.v[w] = from_float<T>(o2);
+            }
+            *reinterpret_cast<Piece*>(dst + half) = turned;
+        } else {
+#pragma unroll
+            for (int w = 0; w < W; ++w) made.v[w] = from_float<T>(x[w]);
+        }
         *reinterpret_cast<Piece*>(dst) = made;
     }
 }
@@ -97,9 +105,9 @@ void launch_bias_rope_cache(const void* qkv, const float* bias, const int* posit
                             int q_units, int k_units, int v_heads, int maps, int d, int dv, int rotary_dim,
                             int page_size, cudaStream_t stream) {
     // Many tokens: a block takes all of a token's row, so that its cosines and sines are formed once; few tokens:
-    // a piece to a thread, so that the launch has blocks enough.
+    // an item to a thread, so that the launch has blocks enough.
     const int threads = 256;
-    const int pieces = ((q_units + k_units) * d + v_heads * dv) / W;
+    const int pieces = ((q_units + k_units) * (d - rotary_dim / 2) + v_heads * dv) / W;
     const int pieces_per_block = num_tokens >= 256 ? pieces : threads;
     dim3 grid(num_tokens, (pieces + pieces_per_block - 1) / pieces_per_block);
     const size_t smem = sizeof(float) * (size_t)rotary_dim;
