@@ -597,8 +597,15 @@ def test_toy_arrangements_with_four_norms_and_without_a_feed_forward():
             DecoderModel(dataclasses.replace(base, layers=(dataclasses.replace(sandwich, norms=base.layers[0].norms),
                                                            mixer_only)), torch.float32, "cpu")
         with pytest.raises(ValueError, match="needs a feed-forward"):
+            DecoderModel(dataclasses.replace(base, layers=(dataclasses.replace(sandwich, feed_forward=None),
+                                                           mixer_only)), torch.float32, "cpu")
+        # the pre-norm arrangement takes a layer without a feed-forward, which then brings the mixer's norm alone
+        with pytest.raises(ValueError, match="arranges norms"):
             DecoderModel(dataclasses.replace(base, layers=(dataclasses.replace(base.layers[0], feed_forward=None),
                                                            mixer_only)), torch.float32, "cpu")
+        DecoderModel(dataclasses.replace(base, layers=(dataclasses.replace(
+            base.layers[0], feed_forward=None, norms={"mixer": base.layers[0].norms["mixer"]}), mixer_only)),
+            torch.float32, "cpu")
         runner = ModelRunner(spec, weights, "float32", 8, 16, 2, device="cuda")
         cfg = {"heads": 4, "kv_heads": 2, "head_dim": 16, "eps": 1e-6, "theta": 1e4}
         tokens = helpers.random_tokens(97, 29, seed=12)
