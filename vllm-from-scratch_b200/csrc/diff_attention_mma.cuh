@@ -90,12 +90,36 @@ __device__ __forceinline__ void load_list_tile(bf16* k_s, bf16* v_s, const bf16*
     }
 }
 
-// cap * tanh(x / cap) in units of log2 e, from one exponential and one division: tanh(y) = 1 - 2 / (e^(2 y) + 1).
+// 2^x by the special-function unit alone (two units in the last place; results below 2^-126 are zero, which a
+// softmax weight may be).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float fast_reciprocal(float x) {
+    float y;
+    asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+// What turns a raw product q . k into the capped score in units of log2 e: with a cap, `in` = scale * 2 log2 e /
+// cap and `out` = cap * log2 e; without, `in` = scale * log2 e and `out` = 0.
+struct ScoreScale {
+    float in, out;
+};
+__device__ __forceinline__ ScoreScale score_scale(float scale, float cap) {
+    ScoreScale made;
+    made.in = cap > 0.0f ? scale * (2.0f * kLog2e) / cap : scale * kLog2e;
+    made.out = cap > 0.0f ? cap * kLog2e : 0.0f;
+    return made;
+}
+// cap * tanh(s / cap) in units of log2 e, from one exponential and one reciprocal: tanh(y) = 1 - 2 / (e^(2 y) + 1).
 // Its absolute error is a few units in the last place of 1, times cap.
-__device__ __forceinline__ float capped_log2(float x, float cap, float inv_cap) {
-    if (cap <= 0.0f) return x * kLog2e;
-    const float e = exp2f(x * inv_cap * (2.0f * kLog2e));
-    return cap * kLog2e * (1.0f - __fdividef(2.0f, e + 1.0f));
+__device__ __forceinline__ float capped_log2(float raw, const ScoreScale& by) {
+    if (by.out <= 0.0f) return raw * by.in;
+    const float e = fast_exp2(raw * by.in);
+    return fmaf(-2.0f * by.out, fast_reciprocal(e + 1.0f), by.out);
 }
 
 // o += P V for 16 entries of a tile: the weights as three bfloat16 pieces (smallest first), `v_row` this lane's
@@ -178,16 +202,16 @@ __device__ __forceinline__ void softmax_and_values(float (&s)[8][4], float (&o)[
     max_b = quad_max(max_b);
     const float new_a = fmaxf(m_a, max_a), new_b = fmaxf(m_b, max_b);
     const float ref_a = new_a == -INFINITY ? 0.0f : new_a, ref_b = new_b == -INFINITY ? 0.0f : new_b;
-    const float alpha_a = exp2f(m_a - ref_a), alpha_b = exp2f(m_b - ref_b);
+    const float alpha_a = fast_exp2(m_a - ref_a), alpha_b = fast_exp2(m_b - ref_b);
     m_a = new_a;
     m_b = new_b;
     float sum_a = 0.0f, sum_b = 0.0f;
 #pragma unroll
     for (int nt = 0; nt < 8; ++nt) {
-        s[nt][0] = exp2f(s[nt][0] - ref_a);
-        s[nt][1] = exp2f(s[nt][1] - ref_a);
-        s[nt][2] = exp2f(s[nt][2] - ref_b);
-        s[nt][3] = exp2f(s[nt][3] - ref_b);
+        s[nt][0] = fast_exp2(s[nt][0] - ref_a);
+        s[nt][1] = fast_exp2(s[nt][1] - ref_a);
+        s[nt][2] = fast_exp2(s[nt][2] - ref_b);
+        s[nt][3] = fast_exp2(s[nt][3] - ref_b);
         sum_a += s[nt][0] + s[nt][1];
         sum_b += s[nt][2] + s[nt][3];
     }
@@ -325,7 +349,7 @@ __global__ void __launch_bounds__(kDiffThreads, DV <= 128 ? 2 : 1) diff_prefill_
     const KeyList list = key_list(first_pos, first_pos + rows_here - 1, window, keep_first);
     const int entries = list.count();
     const int tiles = (entries + kKeys - 1) / kKeys;
-    const float inv_cap = p.softcap > 0.0f ? 1.0f / p.softcap : 0.0f;
+    const ScoreScale by = score_scale(p.scale, p.softcap);
 
     auto k_stage = [&](int s) { return stage_base + (size_t)s * kStage; };
     auto v_stage = [&](int s) { return stage_base + (size_t)s * kStage + kKeys * (2 * D + kDiffPad); };
@@ -369,7 +393,7 @@ __global__ void __launch_bounds__(kDiffThreads, DV <= 128 ? 2 : 1) diff_prefill_
             for (int nt = 0; nt < 8; ++nt)
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    float v = capped_log2(s[nt][e] * p.scale, p.softcap, inv_cap);
+                    float v = capped_log2(s[nt][e], by);
                     if (!all_visible) {
                         const int entry = e0 + nt * 8 + (lane & 3) * 2 + (e & 1);
                         const int kp = list.position(entry);
@@ -445,7 +469,7 @@ __global__ void __launch_bounds__(kDiffThreads) diff_decode_mma_kernel(
     const int my_end = min(entries, my_begin + chunk);
     const int tiles = my_end > my_begin ? (my_end - my_begin + kKeys - 1) / kKeys : 0;
     const int* table = p.block_table + (size_t)request * p.max_pages;
-    const float inv_cap = p.softcap > 0.0f ? 1.0f / p.softcap : 0.0f;
+    const ScoreScale by = score_scale(p.scale, p.softcap);
 
     const int row_a = lane >> 2, row_b = row_a + 8;
     const bf16* q_base = q + ((size_t)request * nq + (size_t)kv_head * group) * (2 * D) + map * D;
@@ -511,7 +535,7 @@ __global__ void __launch_bounds__(kDiffThreads) diff_decode_mma_kernel(
 #pragma unroll
             for (int e = 0; e < 2 * kHalves; ++e) {
                 const int entry = e0 + part * 16 + nt * 8 + (lane & 3) * 2 + (e & 1);
-                float v = capped_log2(s[nt][e] * p.scale, p.softcap, inv_cap);
+                float v = capped_log2(s[nt][e], by);
                 if (entry >= my_end) v = -INFINITY;       // every entry of the list is visible to the one query
                 s[nt][e] = v;
                 if (e < 2) max_a = fmaxf(max_a, v); else max_b = fmaxf(max_b, v);
@@ -519,13 +543,13 @@ __global__ void __launch_bounds__(kDiffThreads) diff_decode_mma_kernel(
         max_a = quad_max(max_a);
         const float new_a = fmaxf(m_a, max_a);
         const float ref_a = new_a == -INFINITY ? 0.0f : new_a;
-        const float alpha_a = exp2f(m_a - ref_a);
+        const float alpha_a = fast_exp2(m_a - ref_a);
         m_a = new_a;
         float sum_a = 0.0f;
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
-            s[nt][0] = exp2f(s[nt][0] - ref_a);
-            s[nt][1] = exp2f(s[nt][1] - ref_a);
+            s[nt][0] = fast_exp2(s[nt][0] - ref_a);
+            s[nt][1] = fast_exp2(s[nt][1] - ref_a);
             sum_a += s[nt][0] + s[nt][1];
         }
         l_a = l_a * alpha_a + sum_a;
@@ -534,13 +558,13 @@ __global__ void __launch_bounds__(kDiffThreads) diff_decode_mma_kernel(
             max_b = quad_max(max_b);
             const float new_b = fmaxf(m_b, max_b);
             const float ref_b = new_b == -INFINITY ? 0.0f : new_b;
-            alpha_b = exp2f(m_b - ref_b);
+            alpha_b = fast_exp2(m_b - ref_b);
             m_b = new_b;
             float sum_b = 0.0f;
 #pragma unroll
             for (int nt = 0; nt < 2; ++nt) {
-                s[nt][2] = exp2f(s[nt][2] - ref_b);
-                s[nt][3] = exp2f(s[nt][3] - ref_b);
+                s[nt][2] = fast_exp2(s[nt][2] - ref_b);
+                s[nt][3] = fast_exp2(s[nt][3] - ref_b);
                 sum_b += s[nt][2] + s[nt][3];
             }
             l_b = l_b * alpha_b + sum_b;
