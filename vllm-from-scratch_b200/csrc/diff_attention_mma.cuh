@@ -217,9 +217,12 @@ __device__ __forceinline__ void softmax_and_values(float (&s)[8][4], float (&o)[
     }
     l_a = l_a * alpha_a + sum_a;
     l_b = l_b * alpha_b + sum_b;
+    // once the maxima have settled a tile changes none of them: the factors are all 1 and the output stays
+    if (__any_sync(0xffffffffu, alpha_a != 1.0f || alpha_b != 1.0f)) {
 #pragma unroll
-    for (int nt = 0; nt < DV / 8; ++nt) {
-        o[nt][0] *= alpha_a; o[nt][1] *= alpha_a; o[nt][2] *= alpha_b; o[nt][3] *= alpha_b;
+        for (int nt = 0; nt < DV / 8; ++nt) {
+            o[nt][0] *= alpha_a; o[nt][1] *= alpha_a; o[nt][2] *= alpha_b; o[nt][3] *= alpha_b;
+        }
     }
     const int mi = lane >> 3, ri = lane & 7;
 #pragma unroll
