@@ -160,8 +160,9 @@ class HyperConnectionBlock(Block):
         self.norm_roles = ("mixer", "feed_forward") if feed_forward is not None else ("mixer",)
         super().__init__(params, env, mixer=mixer, feed_forward=feed_forward, norms=norms)
         self.streams = int(params["streams"])
-        if self.streams < 1:
-            raise ValueError(f"block at {env.prefix!r}: streams={self.streams}")
+        from ..kernels.streams import MAX_STREAMS
+        if not 1 <= self.streams <= MAX_STREAMS:
+            raise ValueError(f"block at {env.prefix!r}: streams={self.streams} (1 to {MAX_STREAMS} are built)")
         self.names = tuple(params.get("names", ("hc1", "hc2")))[:len(self.norm_roles)]
         for role, norm in self.norms.items():
             if not hasattr(norm, "weight") or not hasattr(norm, "eps"):
