@@ -12,8 +12,9 @@
 //
 // The keys a block visits are a list: the first positions that stay visible whatever the window (those that lie
 // before the window of the block's first query), then the window's keys up to the block's last query.  Tiles of
-// 64 entries of that list go through two stages of shared memory by 16-byte asynchronous copies, row by row
-// through the block table.  Rows are padded by 16 bytes, which spreads the eight rows of an ldmatrix over all
+// 64 entries of that list go through two stages of shared memory (three in a decode block) by 16-byte asynchronous
+// copies; where each entry's row lies in the pages is looked up through the block table once an entry, a turn
+// ahead of the tile's copies.  Rows are padded by 16 bytes, which spreads the eight rows of an ldmatrix over all
 // banks for every row length that is a multiple of 32 bytes.
 #pragma once
 
@@ -492,8 +493,8 @@ __global__ void __launch_bounds__(kDiffThreads) diff_decode_mma_kernel(
     auto k_stage = [&](int s) { return stage_base + (size_t)s * kStage; };
     auto v_stage = [&](int s) { return stage_base + (size_t)s * kStage + kKeys * (2 * D + kDiffPad); };
 
-    // A decode block waits for memory and little else: two tiles are on their way while one is used (a group of
-    // copies is committed every turn, an empty one too, so that the count behind the wait is the same every turn).
+    // Two tiles are on their way while one is used (a group of copies is committed every turn, an empty one too,
+    // so that the count behind the wait is the same every turn).
     // Where the rows of tile i lie is looked up a turn before the tile's copies start (slot i % stages).
     long long* row_slots = reinterpret_cast<long long*>(stage_base + kDiffDecodeStages * (size_t)kStage);
     auto rows_of = [&](int tile) { return row_slots + (tile % kDiffDecodeStages) * kKeys; };
