@@ -33,7 +33,7 @@ EXTRA_FLAGS: dict[str, list[str]] = {
 }
 LIBRARIES = ("norm", "rope_cache", "attention_generic", "gemm_f32", "attention_bf16", "gemm_bf16",
              "sampling", "decode_attention_static", "norm_ext", "attention_bias", "recurrence", "grouped", "streams",
-             "diff_attention", "diff_attention_bf16")
+             "diff_attention", "diff_attention_bf16", "qk_prepare")
 # Sources that are compiled for given sizes (``-DNAME=value``): a model builds the sizes that its layers have when
 # it first runs them; the ones listed here are built with everything else.
 Defines = tuple[tuple[str, int], ...]

@@ -223,7 +223,7 @@ __global__ void combine_experts_kernel(const T* __restrict__ rows, const int* __
             for (int j = 0; j < top; ++j) {
                 const int row = position[(size_t)token * top + j];
                 if (row < 0 && !(x != nullptr && ids[(size_t)token * top + j] >= experts)) continue;
-                const float w = weights[(size_t)token * top + j];
+                const float w = weights ? weights[(size_t)token * top + j] : 1.0f;
                 const float4 v = row < 0 ? load_four(x + (size_t)token * width + i) : load_four(rows + (size_t)row * width + i);
                 sum.x = fmaf(w, v.x, sum.x); sum.y = fmaf(w, v.y, sum.y);
                 sum.z = fmaf(w, v.z, sum.z); sum.w = fmaf(w, v.w, sum.w);
@@ -240,9 +240,10 @@ __global__ void combine_experts_kernel(const T* __restrict__ rows, const int* __
         float sum = 0.0f;
         for (int j = 0; j < top; ++j) {
             const int row = position[(size_t)token * top + j];
-            if (row >= 0) sum = fmaf(weights[(size_t)token * top + j], to_float(rows[(size_t)row * width + i]), sum);
+            const float w = weights ? weights[(size_t)token * top + j] : 1.0f;
+            if (row >= 0) sum = fmaf(w, to_float(rows[(size_t)row * width + i]), sum);
             else if (x != nullptr && ids[(size_t)token * top + j] >= experts)
-                sum = fmaf(weights[(size_t)token * top + j], to_float(x[(size_t)token * width + i]), sum);
+                sum = fmaf(w, to_float(x[(size_t)token * width + i]), sum);
         }
         if (extra != nullptr) sum += to_float(extra[(size_t)token * width + i]);
         out[(size_t)token * width + i] = from_float<T>(sum);
@@ -281,7 +282,15 @@ struct GroupedArgs {
     long long a_group, c_group;     // elements between groups within a row
     float act_limit, act_slope, act_offset;     // gated epilogue, see gated_value
     int act_kind;           // 0: silu(gate) * up; 1: capped: g sigmoid(slope g) (u + offset)
+    // A factor per row on the products, ahead of the rounding and of the activation (an expert that is given
+    // weight * x instead of x): indexed like row_index's entries where there is an index, else by the list's row.
+    const float* row_scale;
 };
+
+__device__ __forceinline__ float row_scale_of(const GroupedArgs& p, int list_row) {
+    if (p.row_scale == nullptr) return 1.0f;
+    return p.row_scale[p.row_index ? p.row_index[list_row] : list_row];
+}
 
 __device__ __forceinline__ float gated_value(float gate, float up, const GroupedArgs& p) {
     if (p.act_kind == 0) return gate * sigmoid_fn(gate) * up;
@@ -426,17 +435,18 @@ __global__ void __launch_bounds__(kThreadsG) grouped_gemm_bf16_kernel(const Grou
         const int r = wm * 16 + g + 8 * half;
         if (r >= rows_here) continue;
         bf16* dst = c + (long long)(list_base + row0 + r) * p.ldc;
+        const float factor = row_scale_of(p, list_base + row0 + r);
 #pragma unroll
         for (int t = 0; t < 4; ++t)
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
                 const int n = n0 + wn * 32 + t * 8 + 2 * t4 + e;
                 if (n >= N) continue;
-                float v = acc[0][t][2 * half + e];
+                float v = acc[0][t][2 * half + e] * factor;
                 if (GATED) {
                     // both products are rounded as a projection's output is, then the activation in float32
                     const float gate = __bfloat162float(__float2bfloat16_rn(v));
-                    const float up = __bfloat162float(__float2bfloat16_rn(acc[NB - 1][t][2 * half + e]));
+                    const float up = __bfloat162float(__float2bfloat16_rn(acc[NB - 1][t][2 * half + e] * factor));
                     v = gated_value(gate, up, p);
                 }
                 dst[n] = __float2bfloat16_rn(v);
@@ -552,6 +562,11 @@ __global__ void __launch_bounds__(kThreadsG, 3) grouped_few_rows_bf16_kernel(con
         float v[NB];
 #pragma unroll
         for (int h = 0; h < NB; ++h) v[h] = ((red[0][h][r][col] + red[1][h][r][col]) + red[2][h][r][col]) + red[3][h][r][col];
+        if (p.row_scale != nullptr) {
+            const float factor = row_scale_of(p, list_base + row0 + r);
+#pragma unroll
+            for (int h = 0; h < NB; ++h) v[h] *= factor;
+        }
         float value = v[0];
         if (GATED)
             value = gated_value(__bfloat162float(__float2bfloat16_rn(v[0])), __bfloat162float(__float2bfloat16_rn(v[NB - 1])), p);
@@ -619,11 +634,12 @@ __global__ void __launch_bounds__(kThreadsG) grouped_gemm_f32_kernel(const Group
         const int r = ty * 4 + i;
         if (r >= rows_here) continue;
         float* dst = c + (long long)(list_base + row0 + r) * p.ldc;
+        const float factor = row_scale_of(p, list_base + row0 + r);
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
             const int n = n0 + tx + 16 * j;
             if (n >= N) continue;
-            dst[n] = GATED ? gated_value(acc[0][i][j], acc[NB - 1][i][j], p) : acc[0][i][j];
+            dst[n] = GATED ? gated_value(acc[0][i][j] * factor, acc[NB - 1][i][j] * factor, p) : acc[0][i][j] * factor;
         }
     }
 }
@@ -631,27 +647,29 @@ __global__ void __launch_bounds__(kThreadsG) grouped_gemm_f32_kernel(const Group
 // ------------------------------------------------------------------------ elementwise
 template <typename T>
 __global__ void capped_swish_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int inter, float limit,
-                                        float slope, float offset) {
+                                        float slope, float offset, const float* __restrict__ row_scale,
+                                        const int* __restrict__ row_index) {
     overlap_trigger();
     overlap_wait();
     const size_t token = blockIdx.x;
+    const float f = row_scale ? row_scale[row_index ? row_index[token] : (int)token] : 1.0f;
     const T* row = gate_up + token * 2 * (size_t)inter;
     if (inter % 4 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0) {
         for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * 4; i < inter; i += gridDim.y * blockDim.x * 4) {
             const float4 gv = load_four(row + i), uv = load_four(row + inter + i);
             float4 r;
             float g, u;
-            g = fminf(gv.x, limit); u = fminf(fmaxf(uv.x, -limit), limit); r.x = g * sigmoid_fn(slope * g) * (u + offset);
-            g = fminf(gv.y, limit); u = fminf(fmaxf(uv.y, -limit), limit); r.y = g * sigmoid_fn(slope * g) * (u + offset);
-            g = fminf(gv.z, limit); u = fminf(fmaxf(uv.z, -limit), limit); r.z = g * sigmoid_fn(slope * g) * (u + offset);
-            g = fminf(gv.w, limit); u = fminf(fmaxf(uv.w, -limit), limit); r.w = g * sigmoid_fn(slope * g) * (u + offset);
+            g = fminf(gv.x * f, limit); u = fminf(fmaxf(uv.x * f, -limit), limit); r.x = g * sigmoid_fn(slope * g) * (u + offset);
+            g = fminf(gv.y * f, limit); u = fminf(fmaxf(uv.y * f, -limit), limit); r.y = g * sigmoid_fn(slope * g) * (u + offset);
+            g = fminf(gv.z * f, limit); u = fminf(fmaxf(uv.z * f, -limit), limit); r.z = g * sigmoid_fn(slope * g) * (u + offset);
+            g = fminf(gv.w * f, limit); u = fminf(fmaxf(uv.w * f, -limit), limit); r.w = g * sigmoid_fn(slope * g) * (u + offset);
             store_four(out + token * inter + i, r);
         }
         return;
     }
     for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < inter; i += gridDim.y * blockDim.x) {
-        const float g = fminf(to_float(row[i]), limit);
-        const float u = fminf(fmaxf(to_float(row[inter + i]), -limit), limit);
+        const float g = fminf(to_float(row[i]) * f, limit);
+        const float u = fminf(fmaxf(to_float(row[inter + i]) * f, -limit), limit);
         out[token * inter + i] = from_float<T>(g * sigmoid_fn(slope * g) * (u + offset));
     }
 }
@@ -756,6 +774,7 @@ B200_EXPORT int b200_gather_rows(const void* x, const int* index, int divisor, v
 
 // ids, x, experts: pairs whose expert number is `experts` or more are identity experts, whose output is the
 // token's row of x (both null: there are none).  extra [tokens, width] or null: rows added to every token's sum.
+// weights null: every weight is 1 (experts whose weight went into their input).
 B200_EXPORT int b200_combine_experts(const void* rows, const int* position, const float* weights, void* out,
                                      int tokens, int width, int top, const int* ids, const void* x, int experts,
                                      const void* extra, int dtype, cudaStream_t stream) {
@@ -777,10 +796,12 @@ B200_EXPORT int b200_combine_experts(const void* rows, const int* position, cons
 
 // See GroupedArgs.  `list_rows`: with offsets, the number of rows over all lists (it bounds the grid).
 // gated: 0 plain; 1 silu(gate) * up; 2 the capped form with (limit, slope, offset).
-B200_EXPORT int b200_grouped_gemm(const void* a, const void* w, void* c, const int* offsets, const int* row_index,
-                                  int index_divisor, int rows, int list_rows, int groups, int N, int K,
-                                  long long lda, long long ldc, long long a_group, long long c_group, int gated,
-                                  float limit, float slope, float offset, int dtype, cudaStream_t stream) {
+// row_scale: float32 factors on the rows of the product (see GroupedArgs), or null.
+B200_EXPORT int b200_grouped_gemm_scaled(const void* a, const void* w, void* c, const int* offsets, const int* row_index,
+                                         int index_divisor, int rows, int list_rows, int groups, int N, int K,
+                                         long long lda, long long ldc, long long a_group, long long c_group, int gated,
+                                         float limit, float slope, float offset, const float* row_scale, int dtype,
+                                         cudaStream_t stream) {
     using namespace b200;
     if (groups <= 0 || N <= 0 || K <= 0) return fail("grouped_gemm", "sizes out of range");
     if (row_index != nullptr && (offsets == nullptr || index_divisor <= 0))
@@ -800,6 +821,7 @@ B200_EXPORT int b200_grouped_gemm(const void* a, const void* w, void* c, const i
     p.rows = rows; p.groups = groups; p.N = N; p.K = K; p.lda = lda; p.ldc = ldc; p.a_group = a_group;
     p.c_group = c_group; p.act_limit = limit; p.act_slope = slope; p.act_offset = offset;
     p.act_kind = gated == 2 ? 1 : 0;
+    p.row_scale = row_scale;
     const dim3 grid((unsigned)tiles, n_tiles);
     const int most_rows = offsets ? list_rows : rows;       // of all lists; of every group without lists
     const bool overlap = most_rows <= kOverlapMostRows;
@@ -825,20 +847,36 @@ B200_EXPORT int b200_grouped_gemm(const void* a, const void* w, void* c, const i
     return check_launch("grouped_gemm");
 }
 
-B200_EXPORT int b200_capped_swish_mul(const void* gate_up, void* out, int tokens, int inter, float limit,
-                                      float slope, float offset, int dtype, cudaStream_t stream) {
+B200_EXPORT int b200_grouped_gemm(const void* a, const void* w, void* c, const int* offsets, const int* row_index,
+                                  int index_divisor, int rows, int list_rows, int groups, int N, int K,
+                                  long long lda, long long ldc, long long a_group, long long c_group, int gated,
+                                  float limit, float slope, float offset, int dtype, cudaStream_t stream) {
+    return b200_grouped_gemm_scaled(a, w, c, offsets, row_index, index_divisor, rows, list_rows, groups, N, K, lda, ldc,
+                                    a_group, c_group, gated, limit, slope, offset, nullptr, dtype, stream);
+}
+
+// row_scale (float32, or null) with row_index (int32, or null: the row itself): row r of gate_up is multiplied by
+// row_scale[row_index[r]] ahead of the caps.
+B200_EXPORT int b200_capped_swish_mul_scaled(const void* gate_up, void* out, int tokens, int inter, float limit,
+                                             float slope, float offset, const float* row_scale, const int* row_index,
+                                             int dtype, cudaStream_t stream) {
     using namespace b200;
     if (tokens == 0 || inter == 0) return 0;
     const dim3 grid(tokens, tokens >= 512 ? 1 : min(8, (inter + 1023) / 1024));
     if (dtype == 0)
         launch_overlapped_if(tokens <= kOverlapMostRows, capped_swish_mul_kernel<float>, grid, 256, 0, stream,
-            (const float*)gate_up, (float*)out, inter, limit, slope, offset);
+            (const float*)gate_up, (float*)out, inter, limit, slope, offset, row_scale, row_index);
     else if (dtype == 1)
         launch_overlapped_if(tokens <= kOverlapMostRows, capped_swish_mul_kernel<__nv_bfloat16>, grid, 256, 0, stream,
-            (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, limit, slope, offset);
+            (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out, inter, limit, slope, offset, row_scale, row_index);
     else
         return fail("capped_swish_mul", "dtype must be 0 (float32) or 1 (bfloat16)");
     return check_launch("capped_swish_mul");
+}
+
+B200_EXPORT int b200_capped_swish_mul(const void* gate_up, void* out, int tokens, int inter, float limit,
+                                      float slope, float offset, int dtype, cudaStream_t stream) {
+    return b200_capped_swish_mul_scaled(gate_up, out, tokens, inter, limit, slope, offset, nullptr, nullptr, dtype, stream);
 }
 
 B200_EXPORT int b200_gelu_mul(const void* gate_up, void* out, int tokens, int inter, int dtype, cudaStream_t stream) {

@@ -8,7 +8,8 @@
 //   paired_norm_mean     out = (rms(a) * wa + rms(b) * wb) / 2      (two mixers side by side)
 //   gated_group_norm     out = rms_g(y * silu(z)) * w               (gate first, groups of channels)
 //                        out = rms_g(y) * w * sigmoid(z)            (gate behind the norm)
-//   bigram_embedding     residual = embed[id] + bigram[(prev * a + id * b) mod buckets]
+//                        out = rms_g(y) * w * silu(z)               (gate behind the norm, silu)
+//   bigram_embedding     residual = embed[id] * scale + bigram[(prev * a + id * b) mod buckets]
 //
 // rms(v) = v * rsqrt(mean(v^2) + eps); every statistic, sum and gate in float32.  One block per
 // row (per row and group for the gated form).
@@ -207,7 +208,7 @@ __global__ void paired_norm_mean_vec_kernel(const T* __restrict__ a, const float
 template <typename T, bool GATE_FIRST>
 __global__ void gated_group_norm_vec_kernel(const float* __restrict__ y, const T* __restrict__ gate, int gate_stride,
                                             const float* __restrict__ weight, T* __restrict__ out, int width,
-                                            int group_width, float eps) {
+                                            int group_width, float eps, int silu_behind) {
     overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
     overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
     __shared__ float scratch[33];
@@ -228,6 +229,7 @@ __global__ void gated_group_norm_vec_kernel(const float* __restrict__ y, const T
                 v[step].z *= z.z * sigmoid_f(z.z); v[step].w *= z.w * sigmoid_f(z.w);
             } else {
                 g[step] = make_float4(sigmoid_f(z.x), sigmoid_f(z.y), sigmoid_f(z.z), sigmoid_f(z.w));
+                if (silu_behind) { g[step].x *= z.x; g[step].y *= z.y; g[step].z *= z.z; g[step].w *= z.w; }
             }
             sum_sq += dot4(v[step]);
         }
@@ -255,11 +257,12 @@ inline int vec_threads(int width) {
     return threads * 4 * kRowSteps >= width ? threads : 0;
 }
 
-// GATE_FIRST: v = y * silu(z), out = rms_g(v) * w.  Otherwise out = rms_g(y) * w * sigmoid(z).
+// GATE_FIRST: v = y * silu(z), out = rms_g(v) * w.  Otherwise out = rms_g(y) * w * sigmoid(z), or, with
+// silu_behind, out = rms_g(y) * w * silu(z).
 template <typename T, bool GATE_FIRST>
 __global__ void gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ gate, int gate_stride,
                                         const float* __restrict__ weight, T* __restrict__ out, int width,
-                                        int group_width, float eps) {
+                                        int group_width, float eps, int silu_behind) {
     overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
     overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
     __shared__ float scratch[33];
@@ -282,7 +285,7 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const T* __
         const float z = to_float(g_row[i]);
         float v = y_row[i];
         if (GATE_FIRST) v = v * (z * sigmoid_f(z)) * inv * weight[first + i];
-        else v = v * inv * weight[first + i] * sigmoid_f(z);
+        else v = v * inv * weight[first + i] * (silu_behind ? z * sigmoid_f(z) : sigmoid_f(z));
         o_row[i] = from_float<T>(v);
     }
 }
@@ -296,7 +299,7 @@ __global__ void bigram_embedding_kernel(const T* __restrict__ table, const T* __
                                         const int* __restrict__ token_request, const int* __restrict__ query_start,
                                         const int* __restrict__ slots, int* __restrict__ previous,
                                         float* __restrict__ residual, int hidden, int vocab, int buckets,
-                                        int mul_prev, int mul_cur, int* __restrict__ error_flag) {
+                                        int mul_prev, int mul_cur, float scale, int* __restrict__ error_flag) {
     overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
     overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
     __shared__ int before_s;
@@ -327,7 +330,7 @@ __global__ void bigram_embedding_kernel(const T* __restrict__ table, const T* __
     if (before >= 0) row = ((long long)before * mul_prev + (long long)id * mul_cur) % buckets;
     const T* src = table + (size_t)id * hidden;
     const T* add = bigram + (size_t)row * hidden;
-    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_float(src[i]) + to_float(add[i]);
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = fmaf(to_float(src[i]), scale, to_float(add[i]));
 }
 
 inline int row_threads(int width) {
@@ -401,7 +404,8 @@ B200_EXPORT int b200_paired_norm_mean(const void* a, const float* wa, const void
 }
 
 // y: float32 [tokens, width]; gate: rows of `gate_stride` elements of which the first `width` are the
-// gate; groups equal parts of the width, each normalised by its own root mean square.
+// gate; groups equal parts of the width, each normalised by its own root mean square.  gate_first: 1 = silu of
+// the gate ahead of the norm, 0 = sigmoid of the gate behind it, 2 = silu of the gate behind it.
 B200_EXPORT int b200_gated_group_norm(const float* y, const void* gate, int gate_stride, const float* weight,
                                       void* out, int tokens, int width, int groups, int gate_first, float eps,
                                       int dtype, cudaStream_t stream) {
@@ -410,6 +414,8 @@ B200_EXPORT int b200_gated_group_norm(const float* y, const void* gate, int gate
     if (tokens < 0 || width <= 0 || groups <= 0 || width % groups) return fail("gated_group_norm", "width must divide into the groups");
     if (groups > 65535) return fail("gated_group_norm", "more than 65535 groups");
     const int group_width = width / groups;
+    if (gate_first < 0 || gate_first > 2) return fail("gated_group_norm", "gate form must be 0, 1 or 2");
+    const bool first = gate_first == 1;
     dim3 grid(tokens, groups);
     const uintptr_t addresses = (uintptr_t)y | (uintptr_t)gate | (uintptr_t)weight | (uintptr_t)out;
     if (group_width % 4 == 0 && gate_stride % 4 == 0 && (addresses & 15) == 0 && vec_threads(group_width) > 0 &&
@@ -417,10 +423,10 @@ B200_EXPORT int b200_gated_group_norm(const float* y, const void* gate, int gate
         const int threads = vec_threads(group_width);
 #define B200_VEC(T, FIRST)                                                                                      \
         launch_overlapped_if(tokens <= kOverlapMostRows, gated_group_norm_vec_kernel<T, FIRST>, grid, threads, 0, stream, y, (const T*)gate, gate_stride, weight, \
-                                                                            (T*)out, width, group_width, eps)
-        if (dtype == 0 && gate_first) B200_VEC(float, true);
+                                                                            (T*)out, width, group_width, eps, gate_first == 2 ? 1 : 0)
+        if (dtype == 0 && first) B200_VEC(float, true);
         else if (dtype == 0) B200_VEC(float, false);
-        else if (gate_first) B200_VEC(__nv_bfloat16, true);
+        else if (first) B200_VEC(__nv_bfloat16, true);
         else B200_VEC(__nv_bfloat16, false);
 #undef B200_VEC
         return check_launch("gated_group_norm");
@@ -428,10 +434,10 @@ B200_EXPORT int b200_gated_group_norm(const float* y, const void* gate, int gate
     const int threads = row_threads(group_width);
 #define B200_CASE(T, FIRST)                                                                             \
     launch_overlapped_if(tokens <= kOverlapMostRows, gated_group_norm_kernel<T, FIRST>, grid, threads, 0, stream, y, (const T*)gate, gate_stride, weight, \
-                                                                    (T*)out, width, group_width, eps)
-    if (dtype == 0 && gate_first) B200_CASE(float, true);
+                                                                    (T*)out, width, group_width, eps, gate_first == 2 ? 1 : 0)
+    if (dtype == 0 && first) B200_CASE(float, true);
     else if (dtype == 0) B200_CASE(float, false);
-    else if (dtype == 1 && gate_first) B200_CASE(__nv_bfloat16, true);
+    else if (dtype == 1 && first) B200_CASE(__nv_bfloat16, true);
     else if (dtype == 1) B200_CASE(__nv_bfloat16, false);
     else return fail("gated_group_norm", "dtype must be 0 (float32) or 1 (bfloat16)");
 #undef B200_CASE
@@ -441,7 +447,7 @@ B200_EXPORT int b200_gated_group_norm(const float* y, const void* gate, int gate
 B200_EXPORT int b200_bigram_embedding(const void* table, const void* bigram, const int* ids, const int* positions,
                                       const int* token_request, const int* query_start, const int* slots,
                                       int* previous, float* residual, int num_tokens, int hidden, int vocab,
-                                      int buckets, int mul_prev, int mul_cur, int* error_flag, int dtype,
+                                      int buckets, int mul_prev, int mul_cur, float scale, int* error_flag, int dtype,
                                       cudaStream_t stream) {
     using namespace b200;
     if (num_tokens == 0) return 0;
@@ -450,11 +456,11 @@ B200_EXPORT int b200_bigram_embedding(const void* table, const void* bigram, con
     if (dtype == 0)
         launch_overlapped_if(num_tokens <= kOverlapMostRows, bigram_embedding_kernel<float>, num_tokens, threads, 0, stream,
             (const float*)table, (const float*)bigram, ids, positions, token_request, query_start, slots, previous,
-            residual, hidden, vocab, buckets, mul_prev, mul_cur, error_flag);
+            residual, hidden, vocab, buckets, mul_prev, mul_cur, scale, error_flag);
     else if (dtype == 1)
         launch_overlapped_if(num_tokens <= kOverlapMostRows, bigram_embedding_kernel<__nv_bfloat16>, num_tokens, threads, 0, stream,
             (const __nv_bfloat16*)table, (const __nv_bfloat16*)bigram, ids, positions, token_request, query_start,
-            slots, previous, residual, hidden, vocab, buckets, mul_prev, mul_cur, error_flag);
+            slots, previous, residual, hidden, vocab, buckets, mul_prev, mul_cur, scale, error_flag);
     else
         return fail("bigram_embedding", "dtype must be 0 (float32) or 1 (bfloat16)");
     return check_launch("bigram_embedding");

@@ -7,6 +7,7 @@
 //                              s_t = 1, c = 0, N = key size;
 //   selective scan (SSD)       a_t = exp(-exp(A_log_h) dt_t), dt_t = softplus(dt + bias_h), k_t = B_t,
 //                              q_t = C_t (shared by the heads of a group), v_t = x_t, s_t = dt_t, c = D_h.
+// (Gated linear attention, whose decay is a vector over the rows of S, has a kernel of its own further down.)
 // A block owns 32, 16 or 8 columns of one head's S for the tokens that one request brings in this
 // step (fewer columns, and so more blocks, where a launch would otherwise leave SMs idle): its 256
 // threads hold the rows of those columns in registers, 8, 16 or 32 parts of the rows, the per-token
@@ -331,6 +332,186 @@ inline int set_segments(ScanParams& p, int seg_len, int segs, float* seg_state, 
     return 0;
 }
 
+// ---------------------------------------------------------------------------------------------
+// Gated linear attention: the state of a head decays per key channel,
+//     S <- diag(a_t) S + k_t v_t^T          y_t = S^T (q_t * n^(-1/2))
+// with a_t = sigmoid(z_t)^(1 / tau) = exp(-softplus(-z_t) / tau), z_t = gate[t] + gate_bias (one number per head
+// and key channel, formed in float32 from the projection's output).  q, k and v are taken as projected (no
+// activation).  The launch shape, the staging in tiles of 16 tokens and the order of the sums are those of
+// recurrence_kernel; the decays of a tile lie in shared memory beside its keys, a row of numbers per token.
+struct GatedScanParams {
+    const int* query_start;     // [R + 1]
+    const int* slots;           // [R]
+    float* state;               // [slots + 1, H, N, dv]
+    float* y;                   // [T, H * dv]
+    int heads, n, dv;
+    const void* proj;           // rows [.. q .. k .. v ..] of `stride` elements
+    int stride, off_q, off_k, off_v;
+    const void* gate;           // rows of `gate_stride` elements, the decays' logits at column off_gate
+    int gate_stride, off_gate;
+    const float* gate_bias;     // [H * N] or null
+    float inv_tau, q_scale;
+    int tokens;
+};
+
+template <typename T, int NPT, int COLS>
+__global__ void __launch_bounds__(kScanThreads) gated_linear_kernel(GatedScanParams p) {
+    overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
+    overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
+    extern __shared__ __align__(16) float scan_smem[];
+    constexpr int kScanColumns = COLS, kScanParts = kScanThreads / COLS;
+    constexpr int kRows = NPT * kScanParts;
+    float* k_s = scan_smem;                                         // [tile][kRows]
+    float* q_s = k_s + kScanTile * kRows;                           // [tile][kRows]
+    float* a_s = q_s + kScanTile * kRows;                           // [tile][kRows]
+    float* v_s = a_s + kScanTile * kRows;                           // [tile][COLS]
+    float* part_s = v_s + kScanTile * kScanColumns;                 // [tile][parts][COLS]
+    const int request = blockIdx.x, head = blockIdx.y;
+    const int tid = threadIdx.x, lane = tid % COLS, part = tid / COLS;
+    const int column0 = blockIdx.z * kScanColumns, column = column0 + lane;
+    const bool live = column < p.dv;
+    const int begin = p.query_start[request], end = p.query_start[request + 1];
+    if (begin >= end) return;
+    const int n = p.n;
+    const int row0 = part * NPT;
+    float* state = p.state + (((size_t)p.slots[request] * p.heads + head) * n) * p.dv + column;
+    float S[NPT];
+#pragma unroll
+    for (int i = 0; i < NPT; ++i) S[i] = (live && row0 + i < n) ? state[(size_t)(row0 + i) * p.dv] : 0.0f;
+    const T* proj = (const T*)p.proj;
+    const T* gate = (const T*)p.gate;
+    const size_t y_stride = (size_t)p.heads * p.dv;
+
+    constexpr int kPerKQ = kScanTile * kRows / kScanThreads;
+    constexpr int kPerV = (kScanTile * kScanColumns + kScanThreads - 1) / kScanThreads;
+    float k_r[kPerKQ], q_r[kPerKQ], z_r[kPerKQ], v_r[kPerV];
+    auto fetch = [&](int t0) {
+        const int count = min(kScanTile, end - t0);
+#pragma unroll
+        for (int j = 0; j < kPerKQ; ++j) {
+            const int idx = tid + j * kScanThreads;
+            const int t = idx / kRows, i = idx - t * kRows;
+            float kv = 0.0f, qv = 0.0f, zv = 0.0f;      // rows past n and tokens past the end: zeros (their S stays 0)
+            if (t < count && i < n) {
+                const size_t token = (size_t)(t0 + t);
+                const T* row = proj + token * p.stride;
+                kv = to_float(row[p.off_k + head * n + i]);
+                qv = to_float(row[p.off_q + head * n + i]);
+                zv = to_float(gate[token * p.gate_stride + p.off_gate + head * n + i]);
+                if (p.gate_bias) zv += p.gate_bias[head * n + i];
+            }
+            k_r[j] = kv;
+            q_r[j] = qv;
+            z_r[j] = zv;
+        }
+#pragma unroll
+        for (int j = 0; j < kPerV; ++j) {
+            const int idx = tid + j * kScanThreads;
+            const int t = idx / kScanColumns, c = idx - t * kScanColumns;
+            float v = 0.0f;
+            if (t < count && column0 + c < p.dv)
+                v = to_float(proj[(size_t)(t0 + t) * p.stride + p.off_v + head * p.dv + column0 + c]);
+            v_r[j] = v;
+        }
+    };
+    auto stage = [&]() {
+#pragma unroll
+        for (int j = 0; j < kPerKQ; ++j) {
+            const int idx = tid + j * kScanThreads;
+            k_s[idx] = k_r[j];
+            q_s[idx] = q_r[j] * p.q_scale;
+            a_s[idx] = expf(-softplus_f(-z_r[j]) * p.inv_tau);      // sigmoid(z) ^ (1 / tau), in float32
+        }
+#pragma unroll
+        for (int j = 0; j < kPerV; ++j)
+            if (tid + j * kScanThreads < kScanTile * kScanColumns) v_s[tid + j * kScanThreads] = v_r[j];
+    };
+
+    fetch(begin);
+    for (int t0 = begin; t0 < end; t0 += kScanTile) {
+        const int count = min(kScanTile, end - t0);
+        __syncthreads();            // the tile ahead has been added up and stored
+        stage();
+        __syncthreads();
+        if (t0 + kScanTile < end) fetch(t0 + kScanTile);
+        for (int t = 0; t < count; ++t) {
+            const float v = v_s[t * kScanColumns + lane];
+            const float* k_row = k_s + t * kRows + row0;
+            const float* q_row = q_s + t * kRows + row0;
+            const float* a_row = a_s + t * kRows + row0;
+            float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+            for (int i = 0; i < NPT; i += 4) {
+                const float4 k4 = *reinterpret_cast<const float4*>(k_row + i);
+                const float4 q4 = *reinterpret_cast<const float4*>(q_row + i);
+                const float4 a4 = *reinterpret_cast<const float4*>(a_row + i);
+                S[i] = fmaf(a4.x, S[i], k4.x * v);
+                S[i + 1] = fmaf(a4.y, S[i + 1], k4.y * v);
+                S[i + 2] = fmaf(a4.z, S[i + 2], k4.z * v);
+                S[i + 3] = fmaf(a4.w, S[i + 3], k4.w * v);
+                acc[0] = fmaf(S[i], q4.x, acc[0]);
+                acc[1] = fmaf(S[i + 1], q4.y, acc[1]);
+                acc[2] = fmaf(S[i + 2], q4.z, acc[2]);
+                acc[3] = fmaf(S[i + 3], q4.w, acc[3]);
+            }
+            part_s[(t * kScanParts + part) * kScanColumns + lane] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+        }
+        __syncthreads();
+        for (int idx = tid; idx < count * kScanColumns; idx += blockDim.x) {
+            const int t = idx / kScanColumns, c = idx - t * kScanColumns;
+            if (column0 + c >= p.dv) continue;
+            float total = 0.0f;
+#pragma unroll
+            for (int w = 0; w < kScanParts; ++w) total += part_s[(t * kScanParts + w) * kScanColumns + c];
+            p.y[(size_t)(t0 + t) * y_stride + head * p.dv + column0 + c] = total;
+        }
+    }
+    if (live) {
+#pragma unroll
+        for (int i = 0; i < NPT; ++i)
+            if (row0 + i < n) state[(size_t)(row0 + i) * p.dv] = S[i];
+    }
+}
+
+template <typename T, int NPT, int COLS>
+int launch_gated_rows(const GatedScanParams& p, int requests, cudaStream_t stream) {
+    auto kernel = gated_linear_kernel<T, NPT, COLS>;
+    constexpr int kRows = NPT * kScanThreads / COLS;
+    const size_t smem = sizeof(float) * ((size_t)3 * kScanTile * kRows + kScanTile * COLS + (size_t)kScanTile * kScanThreads);
+    if (smem > 48 * 1024) {
+        cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (status != cudaSuccess) return fail("gated_linear_attention", cudaGetErrorString(status));
+    }
+    dim3 grid(requests, p.heads, (p.dv + COLS - 1) / COLS);
+    launch_overlapped_if(p.tokens <= kOverlapMostRows, kernel, grid, kScanThreads, smem, stream, p);
+    return check_launch("gated_linear_attention");
+}
+
+template <typename T>
+int launch_gated(const GatedScanParams& p, int requests, cudaStream_t stream) {
+    if (p.heads > 65535) return fail("gated_linear_attention", "more than 65535 heads");
+    if ((p.dv + 7) / 8 > 65535) return fail("gated_linear_attention", "value heads too wide");
+    if (p.n > 256) return fail("gated_linear_attention", "a state of more than 256 rows per head is not built");
+    const long long sms = sm_count() > 0 ? sm_count() : 1;
+    int cols = 32;
+    while (cols > 8 && (long long)requests * p.heads * ((p.dv + cols - 1) / cols) < sms && p.n > 32 * (32 / cols)) cols /= 2;
+#define B200_ROWS(NPT, COLS) return launch_gated_rows<T, NPT, COLS>(p, requests, stream)
+    if (cols == 32) {
+        if (p.n <= 32) B200_ROWS(4, 32);
+        if (p.n <= 64) B200_ROWS(8, 32);
+        if (p.n <= 128) B200_ROWS(16, 32);
+        B200_ROWS(32, 32);
+    }
+    if (cols == 16) {
+        if (p.n <= 64) B200_ROWS(4, 16);
+        if (p.n <= 128) B200_ROWS(8, 16);
+        B200_ROWS(16, 16);
+    }
+    if (p.n <= 128) B200_ROWS(4, 8);
+    B200_ROWS(8, 8);
+#undef B200_ROWS
+}
+
 // out[t, c] = silu(bias[c] + sum_i w[i, c] * in[t - (taps - 1 - i), c]) within one request (the taps'
 // weights are handed over tap by tap, [taps, channels], so that a warp reads them side by side); inputs
 // before the step's portion come from the request's state (its last taps - 1 inputs, oldest first,
@@ -475,6 +656,29 @@ B200_EXPORT int b200_selective_scan(const float* xbc, int xbc_width, const void*
     if (dtype == 0) return launch_recurrence<float, true>(p, requests, stream);
     if (dtype == 1) return launch_recurrence<__nv_bfloat16, true>(p, requests, stream);
     return fail("selective_scan", "dtype must be 0 (float32) or 1 (bfloat16)");
+}
+
+// Gated linear attention over the packed projection `proj` [T, stride] = [.. q .. k .. v ..] (columns off_q, off_k,
+// off_v; q and k are heads x n, v heads x dv; no activation, q times q_scale).  The decays' logits are the
+// columns off_gate .. off_gate + heads * n of `gate` [T, gate_stride] (same dtype as proj), plus gate_bias
+// (float32 [heads * n] or null); decay = sigmoid(logit) ^ inv_tau.  y: float32 [T, heads * dv].  state: float32
+// [slots + 1, heads, n, dv].
+B200_EXPORT int b200_gated_linear_attention(const void* proj, int stride, int off_q, int off_k, int off_v,
+                                            const void* gate, int gate_stride, int off_gate, const float* gate_bias,
+                                            float inv_tau, float q_scale, const int* query_start, const int* slots,
+                                            float* state, float* y, int tokens, int requests, int heads, int n, int dv,
+                                            int dtype, cudaStream_t stream) {
+    using namespace b200;
+    if (requests == 0) return 0;
+    GatedScanParams p = {};
+    p.query_start = query_start; p.slots = slots; p.state = state; p.y = y;
+    p.heads = heads; p.n = n; p.dv = dv; p.tokens = tokens;
+    p.proj = proj; p.stride = stride; p.off_q = off_q; p.off_k = off_k; p.off_v = off_v;
+    p.gate = gate; p.gate_stride = gate_stride; p.off_gate = off_gate; p.gate_bias = gate_bias;
+    p.inv_tau = inv_tau; p.q_scale = q_scale;
+    if (dtype == 0) return launch_gated<float>(p, requests, stream);
+    if (dtype == 1) return launch_gated<__nv_bfloat16>(p, requests, stream);
+    return fail("gated_linear_attention", "dtype must be 0 (float32) or 1 (bfloat16)");
 }
 
 // The convolution reads the state, the second kernel replaces it: call them in this order.

@@ -452,5 +452,5 @@ def mask_tokens(logits: torch.Tensor, rows: torch.Tensor, tokens: torch.Tensor) 
 
 # ---------------------------------------------------- mixers beyond rotary softmax attention
 from .mixing import (add_normed_rmsnorm, bigram_embedding, biased_paged_attention, causal_conv_silu,  # noqa: E402
-                     decayed_linear_attention, gated_group_norm, head_norm_scale_cache, paired_norm_mean,
-                     selective_scan)
+                     decayed_linear_attention, gated_group_norm, gated_linear_attention, head_gate,
+                     head_norm_scale_cache, paired_norm_mean, qk_prepare_cache, scaled_sum, selective_scan)

@@ -61,15 +61,18 @@ def gather_rows(x: torch.Tensor, index: torch.Tensor, divisor: int, out: torch.T
          _I(rows), _I(width), _I(_code(x.dtype)), _stream())
 
 
-def combine_experts(rows: torch.Tensor, position: torch.Tensor, weights: torch.Tensor, out: torch.Tensor,
+def combine_experts(rows: torch.Tensor, position: torch.Tensor, weights: torch.Tensor | None, out: torch.Tensor,
                     identity: tuple[torch.Tensor, torch.Tensor, int] | None = None,
-                    extra: torch.Tensor | None = None) -> None:
+                    extra: torch.Tensor | None = None, top: int | None = None) -> None:
     """``out[t] = sum_j weights[t, j] * rows[position[t * top + j]]`` in float32, j in order (a pair whose
     position is negative adds nothing).  ``identity = (ids, x, experts)``: a pair whose expert number ``ids[t, j]``
     is ``experts`` or more belongs to an identity expert and adds ``weights[t, j] * x[t]``.  ``extra`` ``[T,
-    width]``: rows added to every token's sum (an expert that every token passes)."""
+    width]``: rows added to every token's sum (an expert that every token passes).  ``weights`` None (with
+    ``top``, the choices a token has): every weight is 1, for experts whose weight went into their input."""
     tokens, width = out.shape
-    top = weights.shape[1]
+    if weights is None and top is None:
+        raise KernelError("combine_experts: without weights, say how many choices a token has (top=)")
+    top = weights.shape[1] if weights is not None else int(top)
     ids = x = experts = 0
     if identity is not None:
         ids = _check("chosen experts", identity[0], torch.int32, (tokens, top))
@@ -77,7 +80,8 @@ def combine_experts(rows: torch.Tensor, position: torch.Tensor, weights: torch.T
         experts = int(identity[2])
     _run("grouped", "b200_combine_experts", _P(_check("expert rows", rows, out.dtype, (None, width))),
          _P(_check("rows of the pairs", position, torch.int32, (tokens * top,))),
-         _P(_check("weights", weights, torch.float32, (tokens, top))), _P(_check("combined output", out, _RUN)),
+         _P(_check("weights", weights, torch.float32, (tokens, top), optional=True)),
+         _P(_check("combined output", out, _RUN)),
          _I(tokens), _I(width), _I(top), _P(ids), _P(x), _I(experts),
          _P(_check("rows added to every sum", extra, out.dtype, (tokens, width), optional=True)),
          _I(_code(out.dtype)), _stream())
@@ -95,23 +99,26 @@ def _gate(gated) -> tuple[int, float, float, float]:
 
 
 def expert_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, offsets: torch.Tensor,
-                row_index: torch.Tensor | None, index_divisor: int = 1, gated=None) -> None:
+                row_index: torch.Tensor | None, index_divisor: int = 1, gated=None,
+                row_scale: torch.Tensor | None = None) -> None:
     """Rows in lists, a matrix per list: for list e (rows ``offsets[e]`` to ``offsets[e + 1]``) ``out[row] =
     x[source(row)] @ w[e]^T``; ``source(row) = row_index[row] // index_divisor`` or, without an index,
     the row itself.  ``w`` is ``[E, N, K]``; ``gated``: ``w`` is ``[E, 2 N, K]`` with the gate rows first and
     ``out = act(gate) * up``: ``"silu"``, or ``("capped", limit, slope, offset)`` for ``g sigmoid(slope g) (u +
-    offset)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``."""
+    offset)`` with ``g = min(gate, limit)``, ``u = clamp(up, -limit, limit)``.  ``row_scale`` (float32): the products
+    of a row are multiplied by ``row_scale[row_index[row]]`` (without an index: ``row_scale[row]``) ahead of their
+    rounding and of the activation, which is the expert given ``scale * x`` in place of ``x``."""
     experts, wn, k = w.shape
     list_rows, n = out.shape
     kind, limit, slope, offset = _gate(gated)
     if wn != (2 * n if kind else n):
         raise KernelError(f"expert matrices {tuple(w.shape)} do not give {n} columns")
-    _run("grouped", "b200_grouped_gemm",
+    _run("grouped", "b200_grouped_gemm_scaled",
          _P(_check("expert input", x, _RUN, (None, k))), _P(_check("expert matrices", w, x.dtype)),
          _P(_check("expert output", out, x.dtype)), _P(_check("list offsets", offsets, torch.int32, (experts + 1,))),
          _P(_check("row index", row_index, torch.int32, (list_rows,), optional=True)), _I(index_divisor), _I(0),
          _I(list_rows), _I(experts), _I(n), _I(k), _L(k), _L(n), _L(0), _L(0), _I(kind), _F(limit), _F(slope),
-         _F(offset), _I(_code(x.dtype)), _stream())
+         _F(offset), _P(_check("row factors", row_scale, torch.float32, optional=True)), _I(_code(x.dtype)), _stream())
 
 
 def head_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, column: int = 0) -> None:
@@ -131,13 +138,17 @@ def head_gemm(x: torch.Tensor, w: torch.Tensor, out: torch.Tensor, column: int =
 
 
 def capped_swish_mul(gate_up: torch.Tensor, out: torch.Tensor, limit: float | None, slope: float,
-                     offset: float) -> None:
+                     offset: float, row_scale: torch.Tensor | None = None,
+                     row_index: torch.Tensor | None = None) -> None:
     """``out = g * sigmoid(slope * g) * (u + offset)`` in float32 with ``g = min(gate_up[:, :I], limit)`` and
-    ``u = clamp(gate_up[:, I:], -limit, limit)`` (``limit`` None: no cap)."""
+    ``u = clamp(gate_up[:, I:], -limit, limit)`` (``limit`` None: no cap).  ``row_scale`` (float32): row r of
+    ``gate_up`` is multiplied by ``row_scale[row_index[r]]`` (without an index: ``row_scale[r]``) ahead of the caps."""
     tokens, inter = out.shape
-    _run("grouped", "b200_capped_swish_mul", _P(_check("gate_up", gate_up, out.dtype, (tokens, 2 * inter))),
+    _run("grouped", "b200_capped_swish_mul_scaled", _P(_check("gate_up", gate_up, out.dtype, (tokens, 2 * inter))),
          _P(_check("activation output", out, _RUN)), _I(tokens), _I(inter),
-         _F(math.inf if limit is None else limit), _F(slope), _F(offset), _I(_code(out.dtype)), _stream())
+         _F(math.inf if limit is None else limit), _F(slope), _F(offset),
+         _P(_check("row factors", row_scale, torch.float32, optional=True)),
+         _P(_check("rows of the factors", row_index, torch.int32, optional=True)), _I(_code(out.dtype)), _stream())
 
 
 def gelu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:

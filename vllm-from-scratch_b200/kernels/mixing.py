@@ -8,6 +8,8 @@ As everywhere in this package there is no CPU or library alternative behind thes
 
 from __future__ import annotations
 
+import ctypes
+
 import torch
 
 from . import _F, _I, _P, _check, _code, _run, _stream, count_launch
@@ -49,11 +51,15 @@ def paired_norm_mean(a: torch.Tensor, wa: torch.Tensor, b: torch.Tensor, wb: tor
 
 
 def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, groups: int,
-                     gate_first: bool, eps: float) -> None:
+                     gate_first: bool, eps: float, silu_behind: bool = False) -> None:
     """``y`` float32 ``[T, W]``; ``gate`` rows whose first W elements are the gate (a view of a
     wider projection will do: only its row stride is used).  ``gate_first``: ``out = rms_g(y *
-    silu(gate)) * weight``; otherwise ``out = rms_g(y) * weight * sigmoid(gate)``; ``rms_g``
-    normalises each of ``groups`` equal parts of a row by its own root mean square."""
+    silu(gate)) * weight``; otherwise ``out = rms_g(y) * weight * sigmoid(gate)`` (``silu_behind``:
+    ``* silu(gate)``); ``rms_g`` normalises each of ``groups`` equal parts of a row by its own root
+    mean square."""
+    if gate_first and silu_behind:
+        from . import KernelError
+        raise KernelError("gated_group_norm: the gate is either ahead of the norm or behind it")
     tokens, width = y.shape
     _check("recurrence output", y, torch.float32)
     _check("gated norm weight", weight, torch.float32, (width,))
@@ -63,15 +69,16 @@ def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, 
         from . import KernelError
         raise KernelError(f"gate: shape {tuple(gate.shape)}, strides {gate.stride()}, dtype {gate.dtype}")
     _run("norm_ext", "b200_gated_group_norm", _P(y.data_ptr()), _P(gate.data_ptr()), _I(gate.stride(0)),
-         _P(weight.data_ptr()), _P(out.data_ptr()), _I(tokens), _I(width), _I(groups), _I(1 if gate_first else 0),
+         _P(weight.data_ptr()), _P(out.data_ptr()), _I(tokens), _I(width), _I(groups),
+         _I(1 if gate_first else 2 if silu_behind else 0),
          _F(eps), _I(_code(out.dtype)), _stream())
 
 
 def bigram_embedding(table: torch.Tensor, bigram: torch.Tensor, ids: torch.Tensor, positions: torch.Tensor,
                      token_request: torch.Tensor, query_start: torch.Tensor, slots: torch.Tensor,
                      previous: torch.Tensor, residual: torch.Tensor, mul_prev: int, mul_cur: int,
-                     error_flag: torch.Tensor) -> None:
-    """``residual[t] = table[ids[t]] + bigram[(before * mul_prev + ids[t] * mul_cur) mod buckets]`` in
+                     error_flag: torch.Tensor, scale: float = 1.0) -> None:
+    """``residual[t] = table[ids[t]] * scale + bigram[(before * mul_prev + ids[t] * mul_cur) mod buckets]`` in
     float32, ``before`` being the token ahead of t in its request: the one in this step, or, for a
     portion's first token, ``previous[slot]``; a sequence's first token takes the table's last row.
     ``previous`` (int32 ``[slots + 1, 1]``) then holds every request's last token."""
@@ -87,7 +94,7 @@ def bigram_embedding(table: torch.Tensor, bigram: torch.Tensor, ids: torch.Tenso
          _P(_check("state slots", slots, torch.int32, (requests,))),
          _P(_check("previous tokens", previous, torch.int32)),
          _P(_check("residual", residual, torch.float32, (tokens, hidden))),
-         _I(tokens), _I(hidden), _I(vocab), _I(buckets), _I(mul_prev), _I(mul_cur),
+         _I(tokens), _I(hidden), _I(vocab), _I(buckets), _I(mul_prev), _I(mul_cur), _F(scale),
          _P(_check("error flag", error_flag, torch.int32)), _I(_code(table.dtype)), _stream())
 
 
@@ -128,6 +135,67 @@ def head_norm_scale_cache(qkv: torch.Tensor, positions: torch.Tensor, slots: tor
          _I(tokens), _I(num_q_heads), _I(num_kv_heads), _I(head_dim), _I(value_dim), _I(page_size),
          _F(eps), _F(coef), _I(every), _I(stride), _I(1 if (unit_norm or q_weight is not None) else 0),
          _I(1 if (unit_norm or k_weight is not None) else 0), _I(_code(dtype)), _stream())
+
+
+NORM_KINDS = {None: 0, "head": 1, "whole": 2}
+
+
+def qk_prepare_cache(qkv: torch.Tensor, bias: torch.Tensor | None, positions: torch.Tensor, slots: torch.Tensor,
+                     q_weight: torch.Tensor | None, k_weight: torch.Tensor | None, norm: str | None, eps: float,
+                     inv_freq: torch.Tensor | None, rotary_dim: int, interleaved: bool, q_out: torch.Tensor,
+                     k_pages: torch.Tensor | None, v_pages: torch.Tensor | None, num_q_heads: int,
+                     num_kv_heads: int, head_dim: int, value_dim: int, page_size: int) -> None:
+    """From the first ``nq d + nkv d + nkv dv`` columns of the projection's rows: ``bias`` added (float32, that
+    many numbers), RMSNorm of queries and keys (``norm``: None, ``"head"`` with weight vectors of ``d`` numbers for
+    all heads, ``"whole"`` over all heads of q and of k at once with weight vectors of ``nq d`` and ``nkv d``
+    numbers; a weight may be None), rotation of the first ``rotary_dim`` numbers of every query and key head by the
+    angles ``position * inv_freq[i]`` (``interleaved``: the pairs are neighbours ``(2i, 2i + 1)``, else halves
+    ``(i, i + rotary_dim / 2)``), queries to ``q_out``, keys and values to their pages at ``slots``.  ``num_kv_heads
+    = 0``: rows of queries alone (a layer that reads another layer's pages)."""
+    tokens, stride = qkv.shape
+    dtype = qkv.dtype
+    width = (num_q_heads + num_kv_heads) * head_dim + num_kv_heads * value_dim
+    if norm not in NORM_KINDS:
+        from . import KernelError
+        raise KernelError(f"qk_prepare_cache: norm {norm!r} (None, 'head' or 'whole')")
+    q_size = (head_dim,) if norm == "head" else (num_q_heads * head_dim,)
+    k_size = (head_dim,) if norm == "head" else (num_kv_heads * head_dim,)
+    store = num_kv_heads > 0 and k_pages is not None
+    _run("qk_prepare", "b200_qk_prepare_cache",
+         _P(_check("qkv", qkv, _RUN)), _P(_check("projection bias", bias, torch.float32, (width,), optional=True)),
+         _P(_check("positions", positions, torch.int32, (tokens,))),
+         _P(_check("slot mapping", slots, torch.int32, (tokens,))),
+         _P(_check("q norm weight", q_weight, torch.float32, q_size, optional=True)),
+         _P(_check("k norm weight", k_weight, torch.float32, k_size, optional=True)),
+         _P(_check("inverse frequencies", inv_freq, torch.float32, (rotary_dim // 2,), optional=True)),
+         _P(_check("q output", q_out, dtype, (tokens, num_q_heads * head_dim))),
+         _P(_check("key pages", k_pages, dtype, (None, num_kv_heads, page_size, head_dim)) if store else 0),
+         _P(_check("value pages", v_pages, dtype, (None, num_kv_heads, page_size, value_dim)) if store else 0),
+         _I(tokens), _I(num_q_heads), _I(num_kv_heads), _I(head_dim), _I(value_dim), _I(page_size), _I(stride),
+         _I(NORM_KINDS[norm]), _I(rotary_dim if inv_freq is not None else 0), _I(1 if interleaved else 0), _F(eps),
+         _I(_code(dtype)), _stream())
+
+
+def head_gate(x: torch.Tensor, gate: torch.Tensor, gate_column: int, out: torch.Tensor, heads: int,
+              factor: float = 1.0) -> None:
+    """``out[t, h, :] = x[t, h, :] * sigmoid(gate[t, gate_column + h]) * factor`` in float32; ``gate`` may be a
+    wider projection of which ``heads`` columns from ``gate_column`` on are the gates.  ``out`` may be ``x``."""
+    tokens, width = x.shape
+    if gate.dim() != 2 or gate.shape[0] != tokens or gate_column < 0 or gate_column + heads > gate.shape[1] or width % heads:
+        from . import KernelError
+        raise KernelError(f"head_gate: {heads} gates at column {gate_column} of rows {tuple(gate.shape)} for {tuple(x.shape)}")
+    _check("gate rows", gate, x.dtype)
+    _run("qk_prepare", "b200_head_gate", _P(_check("heads' outputs", x, _RUN)),
+         _P(gate.data_ptr() + gate_column * gate.element_size()), _I(gate.shape[1]),
+         _P(_check("gated outputs", out, x.dtype, (tokens, width))), _I(tokens), _I(heads), _I(width // heads),
+         _F(factor), _I(_code(x.dtype)), _stream())
+
+
+def scaled_sum(a: torch.Tensor, scale_a: float, b: torch.Tensor, scale_b: float, out: torch.Tensor) -> None:
+    """``out = a * scale_a + b * scale_b`` element by element, in float32."""
+    _run("qk_prepare", "b200_scaled_sum", _P(_check("first addend", a, _RUN)), _F(scale_a),
+         _P(_check("second addend", b, a.dtype, tuple(a.shape))), _F(scale_b),
+         _P(_check("sum", out, a.dtype, tuple(a.shape))), ctypes.c_longlong(a.numel()), _I(_code(a.dtype)), _stream())
 
 
 # Tests set this to False to drive the float32-arithmetic kernel through the same call.
@@ -274,6 +342,33 @@ def decayed_linear_attention(proj: torch.Tensor, offsets: tuple[int, int, int], 
          _I(tokens), _I(requests), _I(heads), _I(key_dim), _I(value_dim), _I(seg_len), _I(segs),
          _P(seg_state.data_ptr() if segs > 1 else 0), _P(seg_decay.data_ptr() if segs > 1 else 0),
          _I(_code(proj.dtype)), _stream())
+
+
+def gated_linear_attention(proj: torch.Tensor, offsets: tuple[int, int, int], gate: torch.Tensor, gate_offset: int,
+                           gate_bias: torch.Tensor | None, tau: float, q_scale: float, query_start: torch.Tensor,
+                           slots: torch.Tensor, state: torch.Tensor, y: torch.Tensor, heads: int, key_dim: int,
+                           value_dim: int) -> None:
+    """Per request and head, token after token: ``S <- diag(a) S + k v^T``, ``y = S^T (q * q_scale)`` with q, k
+    (``heads x key_dim``) and v (``heads x value_dim``) the columns of ``proj`` that start at ``offsets = (q, k,
+    v)``, as projected, and a decay per head and key channel ``a = sigmoid(z) ** (1 / tau)``, ``z`` = the columns
+    ``gate_offset .. gate_offset + heads * key_dim`` of ``gate`` plus ``gate_bias`` (float32), formed in float32.
+    ``state``: float32 ``[slots + 1, heads, key_dim, value_dim]``, read at the request's slot and left advanced;
+    ``y``: float32 ``[T, heads * value_dim]``."""
+    tokens, stride = proj.shape
+    requests = slots.shape[0]
+    if tau <= 0:
+        from . import KernelError
+        raise KernelError(f"gated linear attention: tau={tau} must be positive")
+    _run("recurrence", "b200_gated_linear_attention",
+         _P(_check("projection", proj, _RUN)), _I(stride), _I(offsets[0]), _I(offsets[1]), _I(offsets[2]),
+         _P(_check("decay logits", gate, proj.dtype, (tokens, None))), _I(gate.shape[1]), _I(gate_offset),
+         _P(_check("decay bias", gate_bias, torch.float32, (heads * key_dim,), optional=True)),
+         _F(1.0 / tau), _F(q_scale),
+         _P(_check("query_start", query_start, torch.int32, (requests + 1,))),
+         _P(_check("state slots", slots, torch.int32, (requests,))),
+         _P(_check("state", state, torch.float32, (None, heads, key_dim, value_dim))),
+         _P(_check("recurrence output", y, torch.float32, (tokens, heads * value_dim))),
+         _I(tokens), _I(requests), _I(heads), _I(key_dim), _I(value_dim), _I(_code(proj.dtype)), _stream())
 
 
 def selective_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_offset: int, dt_bias: torch.Tensor,

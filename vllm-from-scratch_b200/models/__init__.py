@@ -1,4 +1,4 @@
 """Architectures: each module turns one family's configuration into a model made
 of parts and registers itself under its config.json name."""
 
-from . import bemuzen, lobuzen, nodopel, qwen3  # noqa: F401
+from . import bemuzen, lobuzen, mupuvik, nodopel, qwen3  # noqa: F401

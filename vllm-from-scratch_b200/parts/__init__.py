@@ -1,6 +1,6 @@
 """Parts a model is put together from, and the model assembled from them."""
 
-from . import attention, block, embedding, feed_forward, latent, norm, paired, position, recurrent, side  # noqa: F401  (register the built-in kinds)
+from . import attention, block, embedding, feed_forward, gated_attention, latent, norm, paired, position, recurrent, side  # noqa: F401  (register the built-in kinds)
 from .base import (BLOCKS, EMBEDDINGS, FEED_FORWARDS, MIXERS, NORMS, OUTPUT_HEADS, POSITION_ENCODINGS, TOKEN_SIDES, Block,
                    CacheView, Embedding, FeedForward, GroupContext, KVPagesNeed, Mixer, Norm, OutputHead, Part,
                    NormedAddend, PartEnv, PositionEncoding, StateNeed, StepContext, TokenSide, WeightInfo)

@@ -44,6 +44,8 @@ class PagedAttention(Mixer):
             raise ValueError(f"head_dim={self.head_dim}: the attention kernels take even sizes up to 512")
         if position.rotary_dim > self.head_dim:
             raise ValueError(f"rotary_dim={position.rotary_dim} exceeds head_dim={self.head_dim}")
+        if getattr(position, "interleaved", False):
+            raise ValueError("this mixer's kernels turn halves of a head, not neighbours: interleaved=False")
         if self.window is not None and self.window <= 0:
             raise ValueError(f"window must be positive, got {self.window}")
         self.qkv: torch.Tensor | None = None
@@ -275,6 +277,8 @@ class DifferentialAttention(Mixer):
                              f"512 are built")
         if position.rotary_dim > self.head_dim:
             raise ValueError(f"rotary_dim={position.rotary_dim} exceeds head_dim={self.head_dim}")
+        if getattr(position, "interleaved", False):
+            raise ValueError("this mixer's kernels turn halves of a head, not neighbours: interleaved=False")
         if self.window is not None and self.window <= 0:
             raise ValueError(f"window must be positive, got {self.window}")
         if self.softcap is not None and self.softcap <= 0:

@@ -21,9 +21,10 @@ import torch
 # --------------------------------------------------------------------- weights
 @dataclass(frozen=True)
 class WeightInfo:
-    """What a part expects of one checkpoint tensor."""
+    """What a part expects of one checkpoint tensor.  A size of None is the checkpoint's to give (a rank that no
+    configuration key names); the part checks in ``load_weights`` that such sizes fit one another."""
 
-    shape: tuple[int, ...]
+    shape: tuple[int | None, ...]
     # "matrix": kept in the run dtype (bfloat16 when serving).
     # "vector": small per-channel tensor used in 32-bit arithmetic, kept in float32.
     # "table":  integer table, kept as int32.

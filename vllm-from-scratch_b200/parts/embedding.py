@@ -53,8 +53,9 @@ class BigramEmbedding(Embedding):
     kernel reads it from the request's slot for the first token of a portion and leaves the
     portion's last token there.
 
-    params: ``vocab_size``, ``buckets``, ``mul_prev``, ``mul_cur``; ``weight_names`` (token table,
-    bigram table; default ``weight``, ``bigram``)."""
+    params: ``vocab_size``, ``buckets``, ``mul_prev``, ``mul_cur``; ``scale`` (the token's row is multiplied
+    by it, the pair's row is not; default 1); ``weight_names`` (token table, bigram table; default
+    ``weight``, ``bigram``)."""
 
     graph_safe = True
 
@@ -63,6 +64,7 @@ class BigramEmbedding(Embedding):
         self.vocab_size = int(params["vocab_size"])
         self.buckets = int(params["buckets"])
         self.mul_prev, self.mul_cur = int(params["mul_prev"]), int(params["mul_cur"])
+        self.scale = float(params.get("scale", 1.0))
         if self.buckets <= 0:
             raise ValueError(f"bigram embedding: buckets={self.buckets}")
         self.names = tuple(params.get("weight_names", ("weight", "bigram")))
@@ -87,7 +89,7 @@ class BigramEmbedding(Embedding):
             raise ValueError("the bigram embedding keeps the previous token per request: it needs its state")
         kernels.bigram_embedding(self.weight, self.bigram, token_ids, ctx.positions, ctx.token_request,
                                  ctx.query_start, ctx.state_slots, cache.state, residual, self.mul_prev,
-                                 self.mul_cur, error_flag)
+                                 self.mul_cur, error_flag, scale=self.scale)
 
     def table(self) -> torch.Tensor:
         return self.weight

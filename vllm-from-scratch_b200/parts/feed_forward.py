@@ -123,7 +123,11 @@ class RoutedExperts(FeedForward):
     scores); the output is the sum of the chosen experts' outputs weighted with their plain scores
     (``renormalise``: divided by their sum + 1e-20).  The last ``identity_experts`` router outputs have no
     tensors: their expert's output is its input.  With ``shared_intermediate_size`` an expert of that width,
-    of the same form, runs for every token and is added unweighted.
+    of the same form, runs for every token and is added unweighted.  ``activation`` gives the experts another
+    form, ``("capped", limit, slope, offset)``: ``down_e(g sigmoid(slope g) (u + offset))`` with ``g = min(gate_e x,
+    limit)`` and ``u = clamp(up_e x, -limit, limit)``; the shared expert has constants of its own
+    (``shared_activation``).  With ``weight_on_input`` a chosen expert's weight multiplies what it is given, not
+    what it returns: the output is the plain sum of ``expert_e(weight_e x)``.
 
     The tokens of a step are put into one list per expert on the device, the experts' products run as two
     grouped kernels over those lists (the first with the activation in its epilogue), and a last kernel adds
@@ -136,7 +140,8 @@ class RoutedExperts(FeedForward):
     (default ``sigmoid``), ``renormalise`` (default False), ``identity_experts`` (default 0; ``num_experts`` counts
     the experts that have tensors, the router has ``num_experts + identity_experts`` outputs),
     ``shared_intermediate_size`` (default None), ``shared_names`` (gate, up, down; default ``shared.gate``,
-    ``shared.up``, ``shared.down``)."""
+    ``shared.up``, ``shared.down``), ``activation`` and ``shared_activation`` (``"silu"``, the default, or
+    ``("capped", limit, slope, offset)``), ``weight_on_input`` (default False)."""
 
     graph_safe = True
 
@@ -159,6 +164,11 @@ class RoutedExperts(FeedForward):
         self.shared_intermediate_size = None if shared is None else int(shared)
         self.shared_names = tuple(params.get("shared_names", ("shared.gate", "shared.up", "shared.down")))
         self.router_outputs = self.num_experts + self.identity_experts
+        self.activation = self._activation(params.get("activation", "silu"))
+        self.shared_activation = self._activation(params.get("shared_activation", "silu"))
+        self.weight_on_input = bool(params.get("weight_on_input", False))
+        if self.weight_on_input and self.identity_experts:
+            raise ValueError("identity experts take their weight on what they return: weight_on_input=False")
         if self.scoring not in ("sigmoid", "softmax"):
             raise ValueError(f"router scores {self.scoring!r}: 'sigmoid' or 'softmax'")
         if self.identity_experts < 0 or self.num_experts < 1:
@@ -173,6 +183,15 @@ class RoutedExperts(FeedForward):
             raise ValueError(f"top={self.top} experts cannot come from {self.group_keep} groups of "
                              f"{self.router_outputs // self.group_count}")
         self.router = self.correction = self.gate_up = self.down = self.shared_gate_up = self.shared_down = None
+
+    @staticmethod
+    def _activation(value):
+        if value == "silu":
+            return "silu"
+        value = tuple(value)
+        if len(value) != 4 or value[0] != "capped":
+            raise ValueError(f"an expert's activation is 'silu' or ('capped', limit, slope, offset), not {value!r}")
+        return ("capped", float(value[1]), float(value[2]), float(value[3]))
 
     def _expert(self, index: int) -> tuple[str, str, str]:
         return tuple(pattern.format(index=index) for pattern in self.expert_names)
@@ -233,22 +252,35 @@ class RoutedExperts(FeedForward):
             grouped.gather_rows(x, sorted_pair, top, gathered)
             gate_up = torch._grouped_mm(gathered, self.gate_up.transpose(1, 2), offs=offsets[1:])
             kernels.count_launch()
-            kernels.silu_mul(gate_up, hidden)
+            scale = (weights, sorted_pair) if self.weight_on_input else (None, None)
+            if self.activation == "silu" and not self.weight_on_input:
+                kernels.silu_mul(gate_up, hidden)
+            elif self.activation == "silu":     # silu is the capped form without a cap: slope 1, nothing added
+                grouped.capped_swish_mul(gate_up, hidden, None, 1.0, 0.0, *scale)
+            else:
+                grouped.capped_swish_mul(gate_up, hidden, *self.activation[1:], *scale)
             rows = torch._grouped_mm(hidden, self.down.transpose(1, 2), offs=offsets[1:])
             kernels.count_launch()
         else:
             rows = torch.empty((tokens * top, self.env.hidden_size), dtype=x.dtype, device=device)
-            grouped.expert_gemm(x, self.gate_up, hidden, offsets, sorted_pair, top, gated="silu")
+            grouped.expert_gemm(x, self.gate_up, hidden, offsets, sorted_pair, top, gated=self.activation,
+                                row_scale=weights if self.weight_on_input else None)
             grouped.expert_gemm(hidden, self.down, rows, offsets, None)
         shared = None
         if self.shared_gate_up is not None:
             inner = torch.empty((tokens, self.shared_intermediate_size), dtype=x.dtype, device=device)
-            kernels.gated_silu_gemm(x, self.shared_gate_up, inner)
+            if self.shared_activation == "silu":
+                kernels.gated_silu_gemm(x, self.shared_gate_up, inner)
+            else:
+                both = torch.empty((tokens, 2 * self.shared_intermediate_size), dtype=x.dtype, device=device)
+                kernels.gemm(x, self.shared_gate_up, both)
+                grouped.capped_swish_mul(both, inner, *self.shared_activation[1:])
             shared = torch.empty((tokens, self.env.hidden_size), dtype=x.dtype, device=device)
             kernels.gemm(inner, self.shared_down, shared)
         out = torch.empty((tokens, self.env.hidden_size), dtype=x.dtype, device=device)
         # An identity expert's pairs have numbers past the lists' (no row: `position` is negative); the last
         # kernel adds the token's own input for them, and the shared expert's row.
         identity = (ids, x, experts) if self.identity_experts else None
-        grouped.combine_experts(rows, position, weights, out, identity=identity, extra=shared)
+        grouped.combine_experts(rows, position, None if self.weight_on_input else weights, out, identity=identity,
+                                extra=shared, top=top)
         return out

@@ -1,6 +1,7 @@
-"""Two mixers side by side on the same input: ``(rms(left(h)) * w_left + rms(right(h)) * w_right) / 2``,
-each branch's output normalised over the model width with a plain weight vector of its own before the
-mean.  The branches are mixers of any registered kind, built from their own :class:`~.spec.PartSpec`;
+"""Two mixers side by side on the same input.  ``combine="norm_mean"`` (the default): ``(rms(left(h)) * w_left +
+rms(right(h)) * w_right) / 2``, each branch's output normalised over the model width with a plain weight vector
+of its own before the mean.  ``combine="weighted_sum"``: ``scales[0] * left(h) + scales[1] * right(h)``, nothing
+else.  The branches are mixers of any registered kind, built from their own :class:`~.spec.PartSpec`;
 their tensors live under the names the specs give (``left`` and ``right`` by default), their cache
 needs are handed on together (at most one of them may keep pages), and each finds its share of the
 layer's :class:`~.base.CacheView`.
@@ -25,8 +26,9 @@ def _join(prefix: str, name: str) -> str:
 @MIXERS.register("paired_mixers")
 class PairedMixers(Mixer):
     """params: ``branches`` (two :class:`~.spec.PartSpec` of mixers; each spec's ``name`` is the segment
-    of its tensors and of its output norm vector ``<name>.<out_name>``), ``eps``, ``out_name`` (default
-    ``out``)."""
+    of its tensors and of its output norm vector ``<name>.<out_name>``), ``combine`` (``norm_mean`` or
+    ``weighted_sum``), for the mean ``eps`` and ``out_name`` (default ``out``), for the sum ``scales`` (two
+    numbers)."""
 
     def __init__(self, params: Mapping[str, Any], env: PartEnv, position: PositionEncoding) -> None:
         super().__init__(params, env, position)
@@ -35,8 +37,14 @@ class PairedMixers(Mixer):
             raise ValueError("paired mixers take two branches, each the spec of a mixer")
         if not all(branch.name for branch in branches) or branches[0].name == branches[1].name:
             raise ValueError("the two branches need names of their own")
-        self.eps = float(params["eps"])
+        self.combine = str(params.get("combine", "norm_mean"))
+        if self.combine not in ("norm_mean", "weighted_sum"):
+            raise ValueError(f"paired mixers combine by 'norm_mean' or 'weighted_sum', not {self.combine!r}")
+        self.eps = float(params.get("eps", 0.0))
         self.out_name = str(params.get("out_name", "out"))
+        self.scales = tuple(float(value) for value in params.get("scales", (1.0, 1.0)))
+        if len(self.scales) != 2:
+            raise ValueError("paired mixers take one scale for each of the two branches")
         self.specs = branches
         self.branches: list[Mixer] = [
             MIXERS.get(branch.kind)(branch.params, PartEnv(env.hidden_size, env.dtype, env.device,
@@ -53,13 +61,15 @@ class PairedMixers(Mixer):
         for spec, branch in zip(self.specs, self.branches):
             for name, info in branch.expected_weights().items():
                 names[_join(spec.name, name)] = info
-            names[_join(spec.name, self.out_name)] = WeightInfo((self.env.hidden_size,), "vector")
+            if self.combine == "norm_mean":
+                names[_join(spec.name, self.out_name)] = WeightInfo((self.env.hidden_size,), "vector")
         return names
 
     def load_weights(self, tensors: Mapping[str, torch.Tensor]) -> None:
         for index, (spec, branch) in enumerate(zip(self.specs, self.branches)):
             branch.load_weights({name: tensors[_join(spec.name, name)] for name in branch.expected_weights()})
-            self.out_weights[index] = tensors[_join(spec.name, self.out_name)]
+            if self.combine == "norm_mean":
+                self.out_weights[index] = tensors[_join(spec.name, self.out_name)]
 
     # -------------------------------------------------------------------- cache
     def _needs(self) -> list[list]:
@@ -97,5 +107,8 @@ class PairedMixers(Mixer):
         left = self.branches[0].forward(x, ctx, self._view(0, cache))
         right = self.branches[1].forward(x, ctx, self._view(1, cache))
         out = torch.empty_like(left)
-        kernels.paired_norm_mean(left, self.out_weights[0], right, self.out_weights[1], self.eps, out)
+        if self.combine == "weighted_sum":
+            kernels.scaled_sum(left, self.scales[0], right, self.scales[1], out)
+        else:
+            kernels.paired_norm_mean(left, self.out_weights[0], right, self.out_weights[1], self.eps, out)
         return out

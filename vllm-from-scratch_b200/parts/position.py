@@ -30,7 +30,9 @@ from .base import POSITION_ENCODINGS, PartEnv, PositionEncoding
 class RotaryPositionEncoding(PositionEncoding):
     """params: ``theta`` (base), ``rotary_dim`` (channels rotated, even),
     ``scaling_factor`` (positions are divided by it; 1.0 = plain), ``frequency_scaling`` (``(factor, low,
-    high, original)`` or None: the stretching of long wavelengths described above)."""
+    high, original)`` or None: the stretching of long wavelengths described above), ``interleaved`` (default
+    False: channel i is turned with channel ``i + rotary_dim / 2``; True: channel 2i with channel 2i + 1.  A mixer's
+    kernel must know the second form; the frequencies are formed in double precision and rounded once with it)."""
 
     graph_safe = True
 
@@ -39,6 +41,7 @@ class RotaryPositionEncoding(PositionEncoding):
         self.theta = float(params["theta"])
         self.rotary_dim = int(params["rotary_dim"])
         self.scaling_factor = float(params.get("scaling_factor", 1.0))
+        self.interleaved = bool(params.get("interleaved", False))
         if self.theta <= 0 or self.rotary_dim <= 0 or self.rotary_dim % 2:
             raise ValueError(f"rotary position encoding: theta={self.theta}, rotary_dim={self.rotary_dim}")
         exponents = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32) / self.rotary_dim
@@ -61,6 +64,9 @@ class RotaryPositionEncoding(PositionEncoding):
                     smooth = (original / wavelength - low) / (high - low)
                     f = (1.0 - smooth) * f / factor + smooth * f
                 made.append(f)
+            inv_freq = torch.tensor(made, dtype=torch.float64).to(torch.float32)
+        elif self.interleaved:
+            made = [self.theta ** (-2.0 * pair / self.rotary_dim) / self.scaling_factor for pair in range(self.rotary_dim // 2)]
             inv_freq = torch.tensor(made, dtype=torch.float64).to(torch.float32)
         self._inv_freq = inv_freq.to(env.device)
 

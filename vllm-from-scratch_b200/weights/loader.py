@@ -77,6 +77,11 @@ def _target_dtype(info: WeightInfo, stored: torch.dtype, run_dtype: torch.dtype)
     return run_dtype
 
 
+def _fits(found: tuple, expected: tuple) -> bool:
+    """Whether a stored shape is the expected one; an expected size of None takes any."""
+    return len(found) == len(expected) and all(e is None or e == f for f, e in zip(found, expected))
+
+
 def check_names(folder: str | Path, expected: Mapping[str, WeightInfo], ignored: set[str]) -> dict[str, Path]:
     """Compare file contents with ``expected``; return name -> file for the wanted tensors."""
     where: dict[str, Path] = {}
@@ -93,7 +98,7 @@ def check_names(folder: str | Path, expected: Mapping[str, WeightInfo], ignored:
     missing = sorted(name for name in expected if name not in where)
     unexpected = sorted(name for name in where if name not in expected and name not in ignored)
     wrong = sorted((name, shapes[name], tuple(info.shape)) for name, info in expected.items()
-                   if name in shapes and shapes[name] != tuple(info.shape))
+                   if name in shapes and not _fits(shapes[name], tuple(info.shape)))
     if missing or unexpected or wrong or other:
         raise WeightLoadError(str(folder), missing, unexpected, wrong, other)
     return {name: where[name] for name in expected}
@@ -126,7 +131,7 @@ def load_weights_from_tensors(model, tensors: Mapping[str, torch.Tensor]) -> Non
     missing = sorted(name for name in expected if name not in tensors)
     unexpected = sorted(name for name in tensors if name not in expected and name not in ignored)
     wrong = sorted((name, tuple(tensors[name].shape), tuple(info.shape)) for name, info in expected.items()
-                   if name in tensors and tuple(tensors[name].shape) != tuple(info.shape))
+                   if name in tensors and not _fits(tuple(tensors[name].shape), tuple(info.shape)))
     if missing or unexpected or wrong:
         raise WeightLoadError("(in memory)", missing, unexpected, wrong, [])
     model.load_weights({
