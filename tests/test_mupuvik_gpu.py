@@ -420,6 +420,17 @@ def test_attention_forms_far_keys_window_edges_and_page_borders(dtype, shape, fo
     kernels.biased_paged_attention(q_out, k_d, v_d, out, i32(starts), i32(lengths), dev(table_t), None, H, G, d, dv,
                                    page, scale, window, sinks=sinks)
     check(out, "float32 arithmetic")
+    # A gate per token and head applied as the rows are written, into the first columns of wider rows.
+    gates = torch.randn(tokens, 3 + H, generator=g).to(dtype)
+    gated = (want.view(tokens, H, dv) * (0.7 * torch.sigmoid(gates[:, 3:].double()))[:, :, None]).reshape(tokens, -1)
+    for cores in (True, False):
+        wide = torch.zeros(tokens, H * dv + 8, dtype=dtype, device="cuda")
+        kernels.biased_paged_attention(q_out, k_d, v_d, wide[:, :H * dv], i32(starts), i32(lengths), dev(table_t), None, H, G,
+                                       d, dv, page, scale, window, max(fresh) if cores else None, max(lengths), 2,
+                                       sinks=sinks, gate=dev(gates), gate_column=3, gate_factor=0.7)
+        diff = (wide[:, :H * dv].cpu().double() - gated).abs().max()
+        assert float(diff) < tol * float(want.abs().max()), ("gated", cores, float(diff))
+        assert not wide[:, H * dv:].any()
     out = torch.empty(2, H * dv, dtype=dtype, device="cuda")                # the single tokens alone: a decode step
     kernels.biased_paged_attention(q_out[:2], k_d, v_d, out, i32(starts[:3]), i32(lengths[:2]), dev(table_t[:2]), None,
                                    H, G, d, dv, page, scale, window, 1, max(lengths), 0, sinks=sinks)

@@ -227,7 +227,7 @@ B200_EXPORT int b200_prefill_attention_tc_bf16(
         launch_overlapped(merge_splits_kernel<kAtD>, (num_tokens - token_offset) * nq, 128, 0, stream,
                           (const float*)(partial_o + first * key_splits * kAtD),
                           (const float*)(partial_ml + first * key_splits * 2),
-                          (bf16*)out + first * kAtD, key_splits, (const float*)nullptr, 1);
+                          (bf16*)out + first * kAtD, key_splits, (const float*)nullptr, 1, OutForm());
         return check_launch("merge_splits");
     }
     return 0;

@@ -150,13 +150,29 @@ __device__ __forceinline__ float inverse_sum_with_sink(float m, float l, float s
     return keep / (l * keep + exp2f(sink_log2 - top));
 }
 
+// How a kernel leaves its rows: a head's output may be multiplied by factor * sigmoid(gate[token, head]) (a gate per
+// token and head, `gate_stride` elements between tokens; null: by nothing), and a token's heads may be written into
+// rows of `out_stride` elements (0: the heads side by side and nothing else, nq * D).
+struct OutForm {
+    const bf16* gate = nullptr;
+    int gate_stride = 0;
+    float factor = 1.0f;
+    int out_stride = 0;
+};
+
+__device__ __forceinline__ float out_gate(const OutForm& form, size_t token, int head) {
+    if (form.gate == nullptr) return 1.0f;
+    const float z = __bfloat162float(form.gate[token * form.gate_stride + head]);
+    return form.factor / (1.0f + expf(-z));
+}
+
 template <int D, bool EXACT = false>
 __global__ void __launch_bounds__(kThreads) decode_attention_kernel(
     const bf16* __restrict__ q, const bf16* __restrict__ k_pages, const bf16* __restrict__ v_pages,
     bf16* __restrict__ out, float* __restrict__ partial_o, float* __restrict__ partial_ml,
     const int* __restrict__ seq_lens, const int* __restrict__ block_table, int max_pages, int nq,
     int nkv, int page_size, float scale_log2, int window, int splits, const float* __restrict__ slopes,
-    const float* __restrict__ sinks, int cache_nkv, int one_tile) {
+    const float* __restrict__ sinks, int cache_nkv, int one_tile, const OutForm form) {
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* stage_base = reinterpret_cast<bf16*>(smem_raw);
     overlap_trigger();
@@ -328,11 +344,14 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(
         }
         const size_t head = (size_t)request * nq + (size_t)kv_head * group + g;
         if (splits == 1) {
+            const int h = kv_head * group + g;
+            bf16* dst = out + (size_t)request * (form.out_stride ? form.out_stride : nq * D) + (size_t)h * D + j;
+            const float gate = out_gate(form, request, h);
             if (EXACT && sinks != nullptr)
-                out[head * D + j] = __float2bfloat16_rn(
-                    acc * inverse_sum_with_sink(m_star, l_sum, sinks[(size_t)kv_head * group + g] * kLog2e));
+                *dst = __float2bfloat16_rn(
+                    acc * inverse_sum_with_sink(m_star, l_sum, sinks[(size_t)kv_head * group + g] * kLog2e) * gate);
             else
-                out[head * D + j] = __float2bfloat16_rn(l_sum > 0.0f ? acc / l_sum : 0.0f);
+                *dst = __float2bfloat16_rn((l_sum > 0.0f ? acc / l_sum : 0.0f) * gate);
         } else {
             partial_o[(head * splits + split) * D + j] = acc;
             if (j == 0) {
@@ -347,10 +366,15 @@ __global__ void __launch_bounds__(kThreads) decode_attention_kernel(
 // are fetched in one go (every load issued before any is used); more run through a loop.
 template <int D>
 __global__ void merge_splits_kernel(const float* __restrict__ partial_o, const float* __restrict__ partial_ml,
-                                    bf16* __restrict__ out, int splits, const float* __restrict__ sinks, int nq) {
+                                    bf16* __restrict__ out, int splits, const float* __restrict__ sinks, int nq,
+                                    const OutForm form) {
     overlap_trigger();
     overlap_wait();
     const size_t head = blockIdx.x;
+    const size_t token = head / nq;
+    const int h = (int)(head - token * nq);
+    bf16* dst = out + token * (form.out_stride ? form.out_stride : nq * D) + (size_t)h * D;
+    const float gate = out_gate(form, token, h);
     // A sink joins the sum once, here, where a row's splits meet.
     const bool has_sink = sinks != nullptr;
     const float sink_log2 = has_sink ? sinks[head % nq] * kLog2e : 0.0f;
@@ -379,8 +403,8 @@ __global__ void merge_splits_kernel(const float* __restrict__ partial_o, const f
                     }
                 }
             }
-            out[head * D + j] = __float2bfloat16_rn(has_sink ? acc * inverse_sum_with_sink(m_star, l_sum, sink_log2)
-                                                             : (l_sum > 0.0f ? acc / l_sum : 0.0f));
+            dst[j] = __float2bfloat16_rn((has_sink ? acc * inverse_sum_with_sink(m_star, l_sum, sink_log2)
+                                                   : (l_sum > 0.0f ? acc / l_sum : 0.0f)) * gate);
         }
         return;
     }
@@ -395,8 +419,8 @@ __global__ void merge_splits_kernel(const float* __restrict__ partial_o, const f
                 l_sum += weight * partial_ml[(head * splits + s) * 2 + 1];
             }
         }
-        out[head * D + j] = __float2bfloat16_rn(has_sink ? acc * inverse_sum_with_sink(m_star, l_sum, sink_log2)
-                                                         : (l_sum > 0.0f ? acc / l_sum : 0.0f));
+        dst[j] = __float2bfloat16_rn((has_sink ? acc * inverse_sum_with_sink(m_star, l_sum, sink_log2)
+                                               : (l_sum > 0.0f ? acc / l_sum : 0.0f)) * gate);
     }
 }
 
@@ -411,7 +435,7 @@ __global__ void __launch_bounds__(kThreads, EXACT ? 2 : 3) prefill_attention_ker
     bf16* __restrict__ out, const int* __restrict__ query_start, const int* __restrict__ seq_lens,
     const int* __restrict__ block_table, int num_requests, int max_pages, int nq, int nkv,
     int page_size, float scale_log2, int window, int token_offset, const float* __restrict__ slopes,
-    const float* __restrict__ sinks, int cache_nkv) {
+    const float* __restrict__ sinks, int cache_nkv, const OutForm form) {
     // token_offset: row of q and out at which the first of these requests begins (requests ahead of
     // them in the batch are another launch's); query_start holds rows of the whole batch.
     extern __shared__ __align__(128) unsigned char smem_raw[];
@@ -591,14 +615,17 @@ __global__ void __launch_bounds__(kThreads, EXACT ? 2 : 3) prefill_attention_ker
         inv_a = inverse_sum_with_sink(m_a, l_a, sink_log2);
         inv_b = inverse_sum_with_sink(m_b, l_b, sink_log2);
     }
-    bf16* out_tile = out + ((size_t)(q_begin + tile_first) * nq + head) * D;
+    const size_t out_stride = form.out_stride ? (size_t)form.out_stride : (size_t)nq * D;
+    bf16* out_tile = out + (size_t)(q_begin + tile_first) * out_stride + (size_t)head * D;
+    if (row_a < rows_here) inv_a *= out_gate(form, (size_t)(q_begin + tile_first + row_a), head);
+    if (row_b < rows_here) inv_b *= out_gate(form, (size_t)(q_begin + tile_first + row_b), head);
 #pragma unroll
     for (int nt = 0; nt < D / 8; ++nt) {
         const int col = nt * 8 + (lane & 3) * 2;
         if (row_a < rows_here)
-            *reinterpret_cast<unsigned*>(out_tile + (size_t)row_a * nq * D + col) = pack_bf16(o[nt][0] * inv_a, o[nt][1] * inv_a);
+            *reinterpret_cast<unsigned*>(out_tile + (size_t)row_a * out_stride + col) = pack_bf16(o[nt][0] * inv_a, o[nt][1] * inv_a);
         if (row_b < rows_here)
-            *reinterpret_cast<unsigned*>(out_tile + (size_t)row_b * nq * D + col) = pack_bf16(o[nt][2] * inv_b, o[nt][3] * inv_b);
+            *reinterpret_cast<unsigned*>(out_tile + (size_t)row_b * out_stride + col) = pack_bf16(o[nt][2] * inv_b, o[nt][3] * inv_b);
     }
 }
 
@@ -607,7 +634,7 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, void*
                   float* partial_ml, const int* seq_lens, const int* block_table, int num_requests,
                   int max_pages, int nq, int nkv, int page_size, float scale, int window, int splits,
                   cudaStream_t stream, const float* slopes = nullptr, const float* sinks = nullptr,
-                  int cache_nkv = 0) {
+                  int cache_nkv = 0, OutForm form = OutForm()) {
     auto kernel = decode_attention_kernel<D, EXACT>;
     if (cache_nkv <= 0) cache_nkv = nkv;
     // two stages of a key tile and a value tile; of one tile where the values are the keys themselves, but
@@ -624,12 +651,12 @@ int launch_decode(const void* q, const void* k_pages, const void* v_pages, void*
     launch_overlapped(kernel, grid, kThreads, smem, stream,
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, partial_o, partial_ml,
         seq_lens, block_table, max_pages, nq, nkv, page_size, scale * kLog2e, window, splits, slopes, sinks, cache_nkv,
-        one_tile ? 1 : 0);
+        one_tile ? 1 : 0, form);
     if (int rc = check_launch("decode_attention")) return rc;
     if (splits > 1) {
         launch_overlapped(merge_splits_kernel<D>, num_requests * nq, D < 128 ? D : 128, 0, stream,
                           (const float*)partial_o, (const float*)partial_ml, (bf16*)out, splits,
-                          EXACT ? sinks : (const float*)nullptr, nq);
+                          EXACT ? sinks : (const float*)nullptr, nq, form);
         return check_launch("merge_splits");
     }
     return 0;
@@ -640,7 +667,7 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, void
                    const int* query_start, const int* seq_lens, const int* block_table,
                    int num_requests, int num_tokens, int max_pages, int nq, int nkv, int page_size,
                    float scale, int window, int token_offset, cudaStream_t stream, const float* slopes = nullptr,
-                   const float* sinks = nullptr, int cache_nkv = 0) {
+                   const float* sinks = nullptr, int cache_nkv = 0, OutForm form = OutForm()) {
     if (cache_nkv <= 0) cache_nkv = nkv;
     auto kernel = prefill_attention_kernel<D, EXACT>;
     const int smem = 2 * 2 * kKeys * D * (int)sizeof(bf16);
@@ -650,7 +677,7 @@ int launch_prefill(const void* q, const void* k_pages, const void* v_pages, void
     kernel<<<grid, kThreads, smem, stream>>>(
         (const bf16*)q, (const bf16*)k_pages, (const bf16*)v_pages, (bf16*)out, query_start, seq_lens,
         block_table, num_requests, max_pages, nq, nkv, page_size, scale * kLog2e, window, token_offset, slopes,
-        sinks, cache_nkv);
+        sinks, cache_nkv, form);
     return check_launch("prefill_attention");
 }
 

@@ -83,7 +83,8 @@ __global__ void __launch_bounds__(kWarps * 32) biased_paged_attention_kernel(
     const T* __restrict__ q, const T* __restrict__ k_pages, const T* __restrict__ v_pages,
     T* __restrict__ out, const int* __restrict__ query_start, const int* __restrict__ seq_lens,
     const int* __restrict__ block_table, const float* __restrict__ slopes, const float* __restrict__ sinks,
-    int num_requests, int max_pages, int nq, int nkv, int d, int dv, int page_size, float scale, int window) {
+    int num_requests, int max_pages, int nq, int nkv, int d, int dv, int page_size, float scale, int window,
+    const T* __restrict__ gate, int gate_stride, float gate_factor, int out_stride) {
     overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
     overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
     extern __shared__ float smem[];
@@ -205,7 +206,10 @@ __global__ void __launch_bounds__(kWarps * 32) biased_paged_attention_kernel(
             const float keep = expf(row_max[r] - top);
             inv = keep / (row_sum[r] * keep + expf(sink - top));
         }
-        T* dst = out + ((size_t)(q_begin + tile_first + row) * nq + head) * dv;
+        const size_t token = (size_t)(q_begin + tile_first + row);
+        // a gate per token and head on the head's output, and rows that may be wider than the heads side by side
+        if (gate != nullptr) inv *= gate_factor / (1.0f + expf(-to_float(gate[token * gate_stride + head])));
+        T* dst = out + token * (out_stride ? (size_t)out_stride : (size_t)nq * dv) + (size_t)head * dv;
 #pragma unroll
         for (int i = 0; i < DPL; ++i) {
             const int j = lane + 32 * i;
@@ -218,7 +222,8 @@ template <typename T, int DPL>
 int launch_biased(const void* q, const void* k_pages, const void* v_pages, void* out, const int* query_start,
                   const int* seq_lens, const int* block_table, const float* slopes, const float* sinks,
                   int num_requests, int num_tokens, int max_pages, int nq, int nkv, int d, int dv, int page_size,
-                  float scale, int window, cudaStream_t stream) {
+                  float scale, int window, const void* gate, int gate_stride, float gate_factor, int out_stride,
+                  cudaStream_t stream) {
     auto kernel = biased_paged_attention_kernel<T, DPL>;
     const size_t smem = sizeof(float) * ((size_t)kQueryTile * d + (size_t)kKeyTile * (d + 1) + (size_t)kKeyTile * dv);
     if (smem > 48 * 1024) {
@@ -228,7 +233,8 @@ int launch_biased(const void* q, const void* k_pages, const void* v_pages, void*
     dim3 grid(num_tokens / kQueryTile + num_requests, nq);
     launch_overlapped_if(num_tokens <= kOverlapMostRows, kernel, grid, kWarps * 32, smem, stream,
         (const T*)q, (const T*)k_pages, (const T*)v_pages, (T*)out, query_start, seq_lens, block_table, slopes, sinks,
-        num_requests, max_pages, nq, nkv, d, dv, page_size, scale, window);
+        num_requests, max_pages, nq, nkv, d, dv, page_size, scale, window, (const T*)gate, gate_stride, gate_factor,
+        out_stride);
     return check_launch("biased_paged_attention");
 }
 
@@ -236,12 +242,13 @@ template <typename T>
 int dispatch_biased(const void* q, const void* k_pages, const void* v_pages, void* out, const int* query_start,
                     const int* seq_lens, const int* block_table, const float* slopes, const float* sinks,
                     int num_requests, int num_tokens, int max_pages, int nq, int nkv, int d, int dv, int page_size,
-                    float scale, int window, cudaStream_t stream) {
+                    float scale, int window, const void* gate, int gate_stride, float gate_factor, int out_stride,
+                    cudaStream_t stream) {
 #define B200_CASE(DPL)                                                                                       \
     if (dv <= 32 * DPL)                                                                                      \
         return launch_biased<T, DPL>(q, k_pages, v_pages, out, query_start, seq_lens, block_table, slopes,   \
                                      sinks, num_requests, num_tokens, max_pages, nq, nkv, d, dv, page_size,  \
-                                     scale, window, stream);
+                                     scale, window, gate, gate_stride, gate_factor, out_stride, stream);
     B200_CASE(1) B200_CASE(2) B200_CASE(4) B200_CASE(8) B200_CASE(16)
 #undef B200_CASE
     return fail("biased_paged_attention", "value heads above 512 are not built");
@@ -285,12 +292,14 @@ B200_EXPORT int b200_head_norm_scale_cache(
 
 // slopes: float32 [nq] or null (no bias).  sinks: float32 [nq] or null; a head's sink is one more term
 // exp(sink) in its softmax denominator, unscaled, without a key or a value.  window <= 0: every earlier
-// key is visible.
+// key is visible.  gate (run dtype, rows of gate_stride elements, a number per query head) or null: head h's
+// output is multiplied by gate_factor * sigmoid(gate[token, h]).  out_stride: elements between the rows of
+// out (0: nq * dv).
 B200_EXPORT int b200_biased_paged_attention(
     const void* q, const void* k_pages, const void* v_pages, void* out, const int* query_start, const int* seq_lens,
     const int* block_table, const float* slopes, const float* sinks, int num_requests, int num_tokens,
-    int max_pages, int nq, int nkv, int d, int dv, int page_size, float scale, int window, int dtype,
-    cudaStream_t stream) {
+    int max_pages, int nq, int nkv, int d, int dv, int page_size, float scale, int window, const void* gate,
+    int gate_stride, float gate_factor, int out_stride, int dtype, cudaStream_t stream) {
     using namespace b200;
     if (num_requests == 0 || num_tokens == 0) return 0;
     if (nq <= 0 || nkv <= 0 || nq % nkv) return fail("biased_paged_attention", "query heads must be a multiple of key/value heads");
@@ -299,11 +308,11 @@ B200_EXPORT int b200_biased_paged_attention(
     if (dtype == 0)
         return dispatch_biased<float>(q, k_pages, v_pages, out, query_start, seq_lens, block_table, slopes, sinks,
                                       num_requests, num_tokens, max_pages, nq, nkv, d, dv, page_size, scale, window,
-                                      stream);
+                                      gate, gate_stride, gate_factor, out_stride, stream);
     if (dtype == 1)
         return dispatch_biased<__nv_bfloat16>(q, k_pages, v_pages, out, query_start, seq_lens, block_table, slopes,
                                               sinks, num_requests, num_tokens, max_pages, nq, nkv, d, dv, page_size,
-                                              scale, window, stream);
+                                              scale, window, gate, gate_stride, gate_factor, out_stride, stream);
     return fail("biased_paged_attention", "dtype must be 0 (float32) or 1 (bfloat16)");
 }
 
@@ -325,7 +334,7 @@ B200_EXPORT int b200_biased_decode_attention_bf16(
     const void* q, const void* k_pages, const void* v_pages, void* out, float* partial_o, float* partial_ml,
     const int* seq_lens, const int* block_table, const float* slopes, const float* sinks, int num_requests,
     int max_pages, int nq, int nkv, int d, int page_size, float scale, int window, int splits, int cache_nkv,
-    cudaStream_t stream) {
+    const void* gate, int gate_stride, float gate_factor, int out_stride, cudaStream_t stream) {
     using namespace b200;
     if (num_requests == 0) return 0;
     if (cache_nkv <= 0 || nkv % cache_nkv) return fail("biased_decode_attention", "the cached heads must divide the key/value heads");
@@ -333,11 +342,13 @@ B200_EXPORT int b200_biased_decode_attention_bf16(
     if (splits < 1 || nkv > 65535 || num_requests > 65535) return fail("biased_decode_attention", "grid out of range");
     if (splits > 1 && (partial_o == nullptr || partial_ml == nullptr))
         return fail("biased_decode_attention", "scratch for the splits is missing");
+    OutForm form;
+    form.gate = (const bf16*)gate; form.gate_stride = gate_stride; form.factor = gate_factor; form.out_stride = out_stride;
 #define B200_CASE(D)                                                                                         \
     if (d == D)                                                                                              \
         return launch_decode<D, true>(q, k_pages, v_pages, out, partial_o, partial_ml, seq_lens, block_table, \
                                       num_requests, max_pages, nq, nkv, page_size, scale, window, splits,    \
-                                      stream, slopes, sinks, cache_nkv);
+                                      stream, slopes, sinks, cache_nkv, form);
     B200_CASE(64) B200_CASE(128) B200_CASE(256)
 #undef B200_CASE
     return fail("biased_decode_attention", "head_dim not built");
@@ -349,17 +360,20 @@ B200_EXPORT int b200_biased_prefill_attention_bf16(
     const void* q, const void* k_pages, const void* v_pages, void* out, const int* query_start, const int* seq_lens,
     const int* block_table, const float* slopes, const float* sinks, int num_requests, int num_tokens, int max_pages,
     int nq, int nkv, int d, int page_size, float scale, int window, int token_offset, int cache_nkv,
-    cudaStream_t stream) {
+    const void* gate, int gate_stride, float gate_factor, int out_stride, cudaStream_t stream) {
     using namespace b200;
     if (num_requests == 0 || num_tokens - token_offset <= 0) return 0;
     if (cache_nkv <= 0 || nkv % cache_nkv) return fail("biased_prefill_attention", "the cached heads must divide the key/value heads");
     if (token_offset < 0) return fail("biased_prefill_attention", "negative token offset");
     if (!b200_biased_attention_bf16_supports(nq, nkv, d, d)) return fail("biased_prefill_attention", "shape not built");
+    if (out_stride % 2) return fail("biased_prefill_attention", "rows of the output must be an even number of elements apart");
+    OutForm form;
+    form.gate = (const bf16*)gate; form.gate_stride = gate_stride; form.factor = gate_factor; form.out_stride = out_stride;
 #define B200_CASE(D)                                                                                           \
     if (d == D)                                                                                                \
         return launch_prefill<D, true>(q, k_pages, v_pages, out, query_start, seq_lens, block_table,           \
                                        num_requests, num_tokens, max_pages, nq, nkv, page_size, scale, window, \
-                                       token_offset, stream, slopes, sinks, cache_nkv);
+                                       token_offset, stream, slopes, sinks, cache_nkv, form);
     B200_CASE(64) B200_CASE(128) B200_CASE(256)
 #undef B200_CASE
     return fail("biased_prefill_attention", "head_dim not built");

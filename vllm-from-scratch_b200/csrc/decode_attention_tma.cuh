@@ -380,7 +380,7 @@ int launch_decode_tma(const CUtensorMap& map_k, const CUtensorMap& map_v, const 
     if (splits > 1) {
         launch_overlapped(merge_splits_kernel<D>, num_requests * nq, D < 128 ? D : 128, 0, stream,
                           (const float*)partial_o, (const float*)partial_ml, (bf16*)out, splits,
-                          (const float*)nullptr, 1);
+                          (const float*)nullptr, 1, OutForm());
         return check_launch("merge_splits");
     }
     return 0;

@@ -208,7 +208,7 @@ __global__ void paired_norm_mean_vec_kernel(const T* __restrict__ a, const float
 template <typename T, bool GATE_FIRST>
 __global__ void gated_group_norm_vec_kernel(const float* __restrict__ y, const T* __restrict__ gate, int gate_stride,
                                             const float* __restrict__ weight, T* __restrict__ out, int width,
-                                            int group_width, float eps, int silu_behind) {
+                                            int group_width, float eps, int silu_behind, int out_stride) {
     overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
     overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
     __shared__ float scratch[33];
@@ -235,7 +235,7 @@ __global__ void gated_group_norm_vec_kernel(const float* __restrict__ y, const T
         }
     }
     const float inv = rsqrtf(block_sum(sum_sq, scratch) / (float)group_width + eps);
-    T* o_row = out + token * width + first;
+    T* o_row = out + token * out_stride + first;
 #pragma unroll
     for (int step = 0; step < kRowSteps; ++step) {
         const int i = (step * blockDim.x + threadIdx.x) * 4;
@@ -262,7 +262,7 @@ inline int vec_threads(int width) {
 template <typename T, bool GATE_FIRST>
 __global__ void gated_group_norm_kernel(const float* __restrict__ y, const T* __restrict__ gate, int gate_stride,
                                         const float* __restrict__ weight, T* __restrict__ out, int width,
-                                        int group_width, float eps, int silu_behind) {
+                                        int group_width, float eps, int silu_behind, int out_stride) {
     overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
     overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
     __shared__ float scratch[33];
@@ -280,7 +280,7 @@ __global__ void gated_group_norm_kernel(const float* __restrict__ y, const T* __
         sum_sq = fmaf(v, v, sum_sq);
     }
     const float inv = rsqrtf(block_sum(sum_sq, scratch) / (float)group_width + eps);
-    T* o_row = out + token * width + first;
+    T* o_row = out + token * out_stride + first;
     for (int i = threadIdx.x; i < group_width; i += blockDim.x) {
         const float z = to_float(g_row[i]);
         float v = y_row[i];
@@ -404,13 +404,16 @@ B200_EXPORT int b200_paired_norm_mean(const void* a, const float* wa, const void
 }
 
 // y: float32 [tokens, width]; gate: rows of `gate_stride` elements of which the first `width` are the
-// gate; groups equal parts of the width, each normalised by its own root mean square.  gate_first: 1 = silu of
+// gate; out: rows `out_stride` elements apart (0: `width`), of which the first `width` are written; groups
+// equal parts of the width, each normalised by its own root mean square.  gate_first: 1 = silu of
 // the gate ahead of the norm, 0 = sigmoid of the gate behind it, 2 = silu of the gate behind it.
-B200_EXPORT int b200_gated_group_norm(const float* y, const void* gate, int gate_stride, const float* weight,
-                                      void* out, int tokens, int width, int groups, int gate_first, float eps,
-                                      int dtype, cudaStream_t stream) {
+B200_EXPORT int b200_gated_group_norm_rows(const float* y, const void* gate, int gate_stride, const float* weight,
+                                           void* out, int out_stride, int tokens, int width, int groups, int gate_first,
+                                           float eps, int dtype, cudaStream_t stream) {
     using namespace b200;
     if (tokens == 0) return 0;
+    if (out_stride <= 0) out_stride = width;
+    if (out_stride < width) return fail("gated_group_norm", "rows of the output closer than they are wide");
     if (tokens < 0 || width <= 0 || groups <= 0 || width % groups) return fail("gated_group_norm", "width must divide into the groups");
     if (groups > 65535) return fail("gated_group_norm", "more than 65535 groups");
     const int group_width = width / groups;
@@ -418,12 +421,12 @@ B200_EXPORT int b200_gated_group_norm(const float* y, const void* gate, int gate
     const bool first = gate_first == 1;
     dim3 grid(tokens, groups);
     const uintptr_t addresses = (uintptr_t)y | (uintptr_t)gate | (uintptr_t)weight | (uintptr_t)out;
-    if (group_width % 4 == 0 && gate_stride % 4 == 0 && (addresses & 15) == 0 && vec_threads(group_width) > 0 &&
+    if (group_width % 4 == 0 && gate_stride % 4 == 0 && out_stride % 4 == 0 && (addresses & 15) == 0 && vec_threads(group_width) > 0 &&
         (dtype == 0 || dtype == 1)) {
         const int threads = vec_threads(group_width);
 #define B200_VEC(T, FIRST)                                                                                      \
         launch_overlapped_if(tokens <= kOverlapMostRows, gated_group_norm_vec_kernel<T, FIRST>, grid, threads, 0, stream, y, (const T*)gate, gate_stride, weight, \
-                                                                            (T*)out, width, group_width, eps, gate_first == 2 ? 1 : 0)
+                                                                            (T*)out, width, group_width, eps, gate_first == 2 ? 1 : 0, out_stride)
         if (dtype == 0 && first) B200_VEC(float, true);
         else if (dtype == 0) B200_VEC(float, false);
         else if (first) B200_VEC(__nv_bfloat16, true);
@@ -434,7 +437,7 @@ B200_EXPORT int b200_gated_group_norm(const float* y, const void* gate, int gate
     const int threads = row_threads(group_width);
 #define B200_CASE(T, FIRST)                                                                             \
     launch_overlapped_if(tokens <= kOverlapMostRows, gated_group_norm_kernel<T, FIRST>, grid, threads, 0, stream, y, (const T*)gate, gate_stride, weight, \
-                                                                    (T*)out, width, group_width, eps, gate_first == 2 ? 1 : 0)
+                                                                    (T*)out, width, group_width, eps, gate_first == 2 ? 1 : 0, out_stride)
     if (dtype == 0 && first) B200_CASE(float, true);
     else if (dtype == 0) B200_CASE(float, false);
     else if (dtype == 1 && first) B200_CASE(__nv_bfloat16, true);
@@ -442,6 +445,14 @@ B200_EXPORT int b200_gated_group_norm(const float* y, const void* gate, int gate
     else return fail("gated_group_norm", "dtype must be 0 (float32) or 1 (bfloat16)");
 #undef B200_CASE
     return check_launch("gated_group_norm");
+}
+
+// The same with the output's rows side by side.
+B200_EXPORT int b200_gated_group_norm(const float* y, const void* gate, int gate_stride, const float* weight,
+                                      void* out, int tokens, int width, int groups, int gate_first, float eps,
+                                      int dtype, cudaStream_t stream) {
+    return b200_gated_group_norm_rows(y, gate, gate_stride, weight, out, width, tokens, width, groups, gate_first, eps,
+                                      dtype, stream);
 }
 
 B200_EXPORT int b200_bigram_embedding(const void* table, const void* bigram, const int* ids, const int* positions,

@@ -53,7 +53,8 @@ def paired_norm_mean(a: torch.Tensor, wa: torch.Tensor, b: torch.Tensor, wb: tor
 def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, groups: int,
                      gate_first: bool, eps: float, silu_behind: bool = False) -> None:
     """``y`` float32 ``[T, W]``; ``gate`` rows whose first W elements are the gate (a view of a
-    wider projection will do: only its row stride is used).  ``gate_first``: ``out = rms_g(y *
+    wider projection will do: only its row stride is used); ``out`` may be a view of ``W`` columns of wider rows.
+    ``gate_first``: ``out = rms_g(y *
     silu(gate)) * weight``; otherwise ``out = rms_g(y) * weight * sigmoid(gate)`` (``silu_behind``:
     ``* silu(gate)``); ``rms_g`` normalises each of ``groups`` equal parts of a row by its own root
     mean square."""
@@ -63,13 +64,16 @@ def gated_group_norm(y: torch.Tensor, gate: torch.Tensor, weight: torch.Tensor, 
     tokens, width = y.shape
     _check("recurrence output", y, torch.float32)
     _check("gated norm weight", weight, torch.float32, (width,))
-    _check("gated norm output", out, _RUN, (tokens, width))
+    if (not out.is_cuda or out.dtype not in _RUN or tuple(out.shape) != (tokens, width) or out.stride(1) != 1
+            or out.stride(0) < width):
+        from . import KernelError
+        raise KernelError(f"gated norm output: shape {tuple(out.shape)}, strides {out.stride()}, dtype {out.dtype}")
     if gate.dtype != out.dtype or gate.dim() != 2 or gate.shape[0] != tokens or gate.shape[1] < width \
             or gate.stride(1) != 1 or not gate.is_cuda:
         from . import KernelError
         raise KernelError(f"gate: shape {tuple(gate.shape)}, strides {gate.stride()}, dtype {gate.dtype}")
-    _run("norm_ext", "b200_gated_group_norm", _P(y.data_ptr()), _P(gate.data_ptr()), _I(gate.stride(0)),
-         _P(weight.data_ptr()), _P(out.data_ptr()), _I(tokens), _I(width), _I(groups),
+    _run("norm_ext", "b200_gated_group_norm_rows", _P(y.data_ptr()), _P(gate.data_ptr()), _I(gate.stride(0)),
+         _P(weight.data_ptr()), _P(out.data_ptr()), _I(out.stride(0)), _I(tokens), _I(width), _I(groups),
          _I(1 if gate_first else 2 if silu_behind else 0),
          _F(eps), _I(_code(out.dtype)), _stream())
 
@@ -216,11 +220,15 @@ def biased_paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
                            slopes: torch.Tensor | None, num_q_heads: int, num_kv_heads: int, head_dim: int,
                            value_dim: int, page_size: int, scale: float, window: int | None,
                            max_query_len: int | None = None, max_seq_len: int | None = None,
-                           num_decode: int = 0, sinks: torch.Tensor | None = None) -> None:
+                           num_decode: int = 0, sinks: torch.Tensor | None = None,
+                           gate: torch.Tensor | None = None, gate_column: int = 0, gate_factor: float = 1.0) -> None:
     """Causal attention of every request's new queries over its pages with the score ``q . k * scale
     - slopes[h] * (i - j)``; scores, weights and the weighted sum in float32.  ``sinks`` (float32, one
     per query head): ``exp(sinks[h])`` joins the softmax denominator of head h once, unscaled, with no
     key and no value.  ``v_pages`` may be ``k_pages`` itself (keys that serve as the values too).
+    ``gate`` (rows of the run dtype, a number per query head from ``gate_column`` on; a wider projection will do):
+    head h's output is multiplied by ``gate_factor * sigmoid(gate[t, gate_column + h])`` as it is written.
+    ``out`` may be a view of the first ``nq * dv`` columns of wider rows (the heads of another mixer behind them).
 
     bfloat16 with keys and values of one size of 64, 128 or 256 (and ``max_query_len`` and
     ``max_seq_len`` given): the tensor-core kernels, whose softmax weights enter the second product
@@ -235,19 +243,32 @@ def biased_paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
         _check("queries", q, _RUN, (tokens, num_q_heads * head_dim)),
         _check("key pages", k_pages, dtype, (None, num_kv_heads, page_size, head_dim)),
         _check("value pages", v_pages, dtype, (None, num_kv_heads, page_size, value_dim)),
-        _check("attention output", out, dtype, (tokens, num_q_heads * value_dim)),
+        out.data_ptr(),
         _check("query_start", query_start, torch.int32, (requests + 1,)),
         _check("seq_lens", seq_lens, torch.int32, (requests,)),
         _check("block table", block_table, torch.int32, (requests, None)),
         _check("slopes", slopes, torch.float32, (num_q_heads,), optional=True),
         _check("sinks", sinks, torch.float32, (num_q_heads,), optional=True))
+    if (not out.is_cuda or out.dtype != dtype or tuple(out.shape) != (tokens, num_q_heads * value_dim)
+            or (out.stride(1) != 1 and out.shape[1] > 1) or out.stride(0) < out.shape[1]):
+        from . import KernelError
+        raise KernelError(f"attention output: shape {tuple(out.shape)}, strides {out.stride()}, dtype {out.dtype}")
+    out_stride = 0 if out.is_contiguous() else out.stride(0)
+    gate_p, gate_stride = 0, 0
+    if gate is not None:
+        if (gate.dtype != dtype or gate.dim() != 2 or gate.shape[0] != tokens or not gate.is_contiguous()
+                or gate_column < 0 or gate_column + num_q_heads > gate.shape[1]):
+            from . import KernelError
+            raise KernelError(f"gates: {num_q_heads} columns from {gate_column} of rows {tuple(gate.shape)}, dtype {gate.dtype}")
+        gate_p, gate_stride = gate.data_ptr() + gate_column * gate.element_size(), gate.shape[1]
+    form = (_P(gate_p), _I(gate_stride), _F(gate_factor), _I(out_stride))
     # The decode kernel takes up to 16 query heads on a key/value head; more run as several groups that
     # read the same cached head.
     launch_kv = next(m for m in range(num_kv_heads, num_q_heads + 1, num_kv_heads)
                      if num_q_heads % m == 0 and (num_q_heads // m <= 16 or m == num_q_heads))
     if (USE_TENSOR_CORES and dtype == torch.bfloat16 and max_query_len is not None and max_seq_len is not None
             and head_dim == value_dim and head_dim in (64, 128, 256) and num_q_heads % launch_kv == 0
-            and num_q_heads // launch_kv <= 16):
+            and num_q_heads // launch_kv <= 16 and out_stride % 2 == 0):
         from .attention_bf16 import decode_splits
         cached_heads, num_kv_heads = num_kv_heads, launch_kv
         q_p, k_p, v_p, out_p, start_p, lens_p, table_p, slopes_p, sinks_p = checked
@@ -262,22 +283,22 @@ def biased_paged_attention(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torc
             _run("attention_bias", "b200_biased_decode_attention_bf16", _P(q_p), _P(k_p), _P(v_p), _P(out_p),
                  _P(partial_o.data_ptr() if splits > 1 else 0), _P(partial_ml.data_ptr() if splits > 1 else 0),
                  _P(lens_p), _P(table_p), _P(slopes_p), _P(sinks_p), _I(single), _I(width), _I(num_q_heads), _I(num_kv_heads),
-                 _I(head_dim), _I(page_size), _F(scale), _I(window or 0), _I(splits), _I(cached_heads), _stream())
+                 _I(head_dim), _I(page_size), _F(scale), _I(window or 0), _I(splits), _I(cached_heads), *form, _stream())
             if splits > 1:
                 count_launch()
         if single < requests:
             # The requests behind the single tokens: their rows of the block table and of the lengths,
-            # the batch's own q, out and query_start (rows of the whole batch).
+            # the batch's own q, out, gates and query_start (rows of the whole batch).
             _run("attention_bias", "b200_biased_prefill_attention_bf16", _P(q_p), _P(k_p), _P(v_p), _P(out_p),
                  _P(start_p + 4 * single), _P(lens_p + 4 * single), _P(table_p + 4 * single * width), _P(slopes_p),
                  _P(sinks_p),
                  _I(requests - single), _I(tokens), _I(width), _I(num_q_heads), _I(num_kv_heads), _I(head_dim),
-                 _I(page_size), _F(scale), _I(window or 0), _I(single), _I(cached_heads), _stream())
+                 _I(page_size), _F(scale), _I(window or 0), _I(single), _I(cached_heads), *form, _stream())
         return
     _run("attention_bias", "b200_biased_paged_attention",
          *(_P(address) for address in checked),
          _I(requests), _I(tokens), _I(block_table.shape[1]), _I(num_q_heads), _I(num_kv_heads), _I(head_dim),
-         _I(value_dim), _I(page_size), _F(scale), _I(window or 0), _I(_code(dtype)), _stream())
+         _I(value_dim), _I(page_size), _F(scale), _I(window or 0), *form, _I(_code(dtype)), _stream())
 
 
 # ------------------------------------------------------------------ recurrences

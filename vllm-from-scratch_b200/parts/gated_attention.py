@@ -121,8 +121,10 @@ class GatedSoftmaxAttention(Mixer):
     def inner_width(self) -> int:
         return self.num_heads * self.value_dim
 
-    def forward_inner(self, x: torch.Tensor, ctx: StepContext, cache: CacheView, factor: float = 1.0) -> torch.Tensor:
-        """The heads' gated outputs side by side, times ``factor``: what the output product multiplies."""
+    def forward_inner(self, x: torch.Tensor, ctx: StepContext, cache: CacheView, factor: float = 1.0,
+                      out: torch.Tensor | None = None) -> torch.Tensor:
+        """The heads' gated outputs side by side, times ``factor``: what the output product multiplies.  ``out``: where
+        to write them, ``[T, heads * value_dim]``, which may be columns of wider rows."""
         if cache.kind != "pages":
             raise ValueError("attention needs a cache of pages")
         if cache.writable != self.own_kv:
@@ -139,15 +141,17 @@ class GatedSoftmaxAttention(Mixer):
             self.qk_norm_eps, self.position.inverse_frequencies(), self.position.rotary_dim,
             bool(getattr(self.position, "interleaved", False)), q, cache.keys if self.own_kv else None,
             cache.values if self.own_kv else None, nq, nkv if self.own_kv else 0, d, dv, group.page_size)
-        attended = torch.empty((tokens, nq * dv), dtype=x.dtype, device=x.device)
+        attended = out if out is not None else torch.empty((tokens, nq * dv), dtype=x.dtype, device=x.device)
+        factor = factor * self.out_scale
+        # the gate (and the factor with it) is applied where the attention kernel writes a head's output
+        gate = {"gate": projected, "gate_column": projected.shape[1] - nq, "gate_factor": factor} if self.output_gate else {}
         kernels.biased_paged_attention(
             q, cache.keys, cache.values, attended, ctx.query_start, ctx.seq_lens, group.block_table, None,
             nq, nkv, d, dv, group.page_size, self.scale, self.window, ctx.max_query_len, ctx.max_seq_len,
-            ctx.num_decode, sinks=self.sinks)
-        factor = factor * self.out_scale
-        if self.output_gate:
-            kernels.head_gate(attended, projected, projected.shape[1] - nq, attended, nq, factor)
-        elif factor != 1.0:
+            ctx.num_decode, sinks=self.sinks, **gate)
+        if not self.output_gate and factor != 1.0:
+            if not attended.is_contiguous():
+                raise ValueError("an ungated attention with a factor writes rows of its own")
             kernels.scaled_sum(attended, factor, attended, 0.0, attended)
         return attended
 

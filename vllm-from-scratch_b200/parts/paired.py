@@ -1,7 +1,9 @@
 """Two mixers side by side on the same input.  ``combine="norm_mean"`` (the default): ``(rms(left(h)) * w_left +
 rms(right(h)) * w_right) / 2``, each branch's output normalised over the model width with a plain weight vector
 of its own before the mean.  ``combine="weighted_sum"``: ``scales[0] * left(h) + scales[1] * right(h)``, nothing
-else.  The branches are mixers of any registered kind, built from their own :class:`~.spec.PartSpec`;
+else; where both branches end in an output product and can hand over what it multiplies (``forward_inner``,
+``inner_width``, ``out_proj``), the sum is one product: the branches write their rows, each times its scale, side by
+side, and ``[W_left | W_right]`` multiplies them.  The branches are mixers of any registered kind, built from their own :class:`~.spec.PartSpec`;
 their tensors live under the names the specs give (``left`` and ``right`` by default), their cache
 needs are handed on together (at most one of them may keep pages), and each finds its share of the
 layer's :class:`~.base.CacheView`.
@@ -51,6 +53,7 @@ class PairedMixers(Mixer):
                                                            _join(env.prefix, branch.name)), position)
             for branch in branches]
         self.out_weights: list[torch.Tensor | None] = [None, None]
+        self.joined_out: torch.Tensor | None = None
 
     @property
     def graph_safe(self) -> bool:       # a pair may be replayed if both branches may
@@ -70,6 +73,12 @@ class PairedMixers(Mixer):
             branch.load_weights({name: tensors[_join(spec.name, name)] for name in branch.expected_weights()})
             if self.combine == "norm_mean":
                 self.out_weights[index] = tensors[_join(spec.name, self.out_name)]
+        if self.combine == "weighted_sum" and all(
+                hasattr(branch, "forward_inner") and getattr(branch, "out_proj", None) is not None
+                for branch in self.branches):
+            self.joined_out = torch.cat([branch.out_proj for branch in self.branches], dim=1).contiguous()
+            for branch in self.branches:
+                branch.out_proj = None          # held once, in the joined matrix
 
     # -------------------------------------------------------------------- cache
     def _needs(self) -> list[list]:
@@ -104,6 +113,14 @@ class PairedMixers(Mixer):
 
     # ------------------------------------------------------------------ forward
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: CacheView) -> torch.Tensor:
+        if self.joined_out is not None:
+            widths = [branch.inner_width() for branch in self.branches]
+            rows = torch.empty((x.shape[0], sum(widths)), dtype=x.dtype, device=x.device)
+            self.branches[0].forward_inner(x, ctx, self._view(0, cache), self.scales[0], rows[:, :widths[0]])
+            self.branches[1].forward_inner(x, ctx, self._view(1, cache), self.scales[1], rows[:, widths[0]:])
+            out = torch.empty((x.shape[0], self.env.hidden_size), dtype=x.dtype, device=x.device)
+            kernels.gemm(rows, self.joined_out, out)
+            return out
         left = self.branches[0].forward(x, ctx, self._view(0, cache))
         right = self.branches[1].forward(x, ctx, self._view(1, cache))
         out = torch.empty_like(left)

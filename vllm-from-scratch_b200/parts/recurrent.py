@@ -149,8 +149,10 @@ class GatedLinearAttention(Mixer):
     def inner_width(self) -> int:
         return self.inner
 
-    def forward_inner(self, x: torch.Tensor, ctx: StepContext, cache: CacheView, factor: float = 1.0) -> torch.Tensor:
-        """The normalised, gated heads side by side, times ``factor``: what the output product multiplies."""
+    def forward_inner(self, x: torch.Tensor, ctx: StepContext, cache: CacheView, factor: float = 1.0,
+                      out: torch.Tensor | None = None) -> torch.Tensor:
+        """The normalised, gated heads side by side, times ``factor``: what the output product multiplies.  ``out``:
+        where to write them, ``[T, heads * value_dim]``, which may be columns of wider rows."""
         state = cache.states.get("state") if cache.states else cache.state
         if state is None:
             raise ValueError("gated linear attention needs its state slots")
@@ -166,7 +168,7 @@ class GatedLinearAttention(Mixer):
         kernels.gated_linear_attention(proj, (self.inner, self.inner + keys, self.inner + 2 * keys), logits, 0,
                                        self.up_bias, self.tau, self.head_dim ** -0.5, ctx.query_start,
                                        ctx.state_slots, state, y, self.num_heads, self.head_dim, self.value_dim)
-        gated = torch.empty((tokens, self.inner), dtype=x.dtype, device=x.device)
+        gated = out if out is not None else torch.empty((tokens, self.inner), dtype=x.dtype, device=x.device)
         factor = factor * self.out_scale
         if factor not in self._scaled_norms:        # the factor rides on the norm's weights (float32, formed once)
             self._scaled_norms[factor] = (self.norm * factor).contiguous()
