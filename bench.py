@@ -599,7 +599,40 @@ def _nodopel(layers: int, hidden: int, heads: int, inter: int, vocab: int) -> di
     return raw
 
 
-DESIGNS = {"bemuzen": _bemuzen, "lobuzen": _lobuzen, "nodopel": _nodopel}
+def _mupuvik(layers: int, hidden: int, heads: int, inter: int, vocab: int) -> dict:
+    """Layers of the sizes of a Qwen3 layer of this width, in turns of four: attention with the Qwen3 layer's heads
+    (8 key/value heads of 128) and a window of 1024; attention that reads the keys and values of the layer ahead
+    over a window of 512; two mixers side by side (the same heads, half of each rotated, beside gated linear
+    attention of half as many heads of the same sizes); a selective scan of twice the width in heads of 64 with 128
+    rows of state.  Every feed-forward routes a token to 2 of 8 experts of a quarter of the Qwen3 layer's width
+    beside a shared expert of half of it, so that a token passes through as many feed-forward parameters as there."""
+    moe = {"kind": "moe", "expert": {"ff": inter // 4, "limit": 7.0}, "router": {"experts": 8, "top": 2},
+           "shared": {"ff": inter // 2, "limit": 7.0}}
+
+    def attention(window, kv_from=None):
+        mixer = {"heads": heads, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": window}}
+        if kv_from is not None:
+            mixer["kv_from"] = kv_from
+        return {"type": "attention", "mlp": moe, "mixer": mixer}
+
+    parallel = {"type": "parallel", "mlp": moe, "mixer": {
+        "left": {"heads": heads, "kv_heads": 8, "dim": 128, "vdim": 128, "scale": 128 ** -0.5,
+                 "rot": {"base": 1.0e6, "dims": 64}},
+        "right": {"heads": heads // 2, "dim": 128, "vdim": 128, "tau": 16.0}, "left_scale": 0.5, "right_scale": 0.5}}
+    scan = {"type": "mamba2", "mlp": moe, "mixer": {
+        "heads": 2 * hidden // 64, "vdim": 64, "state": 128, "groups": 8, "conv": 4, "norm_groups": 8}}
+    made = []
+    for index in range(layers):
+        place = index % 4
+        made.append(attention(1024) if place == 0 else attention(512, kv_from=index - 1) if place == 1
+                    else parallel if place == 2 else scan)
+    return {"architecture": "Mupuvik", "vocab": vocab, "width": hidden, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0, "bigram": {"buckets": 65521, "mul_prev": 31, "mul_cur": 7}}, "layers": made}
+
+
+DESIGNS = {"bemuzen": _bemuzen, "lobuzen": _lobuzen, "nodopel": _nodopel, "mupuvik": _mupuvik}
+# The model a design is measured beside: Qwen3 layers unless another of the designs is closer kin.
+BESIDE = {"mupuvik": "bemuzen"}
 DESIGN_SIZES = {      # name -> (hidden, heads, feed-forward width)
     "1.7b-layers": (2048, 16, 6144),
     "8b-layers": (4096, 32, 12288),
@@ -643,16 +676,19 @@ def measure_prompt_steps(runner, config, tokens: int) -> dict:
 
 
 def run_design(args, measured, peak_kind) -> dict:
-    """``--design NAME``: prompt steps and decode steps of that design's layers beside Qwen3 layers of the
-    same width, heads, feed-forward, number of layers and vocabulary (random weights, bfloat16)."""
+    """``--design NAME``: prompt steps and decode steps of that design's layers beside Qwen3 layers (Mupuvik: beside
+    Bemuzen layers, the design closest to it) of the same width, heads, feed-forward, number of layers and
+    vocabulary (random weights, bfloat16)."""
     import torch
     layers, vocab, context = args.layers or 4, 32768, args.context or 4096
     design, title = args.design, args.design.capitalize()
     points = {}
     with ClockSampler() as clocks:
         for name, (hidden, heads, inter) in DESIGN_SIZES.items():
-            qwen = dict(_qwen3(layers, hidden, heads, inter, False), vocab_size=vocab)
-            for label, raw in ((design, DESIGNS[design](layers, hidden, heads, inter, vocab)), ("qwen3", qwen)):
+            other = BESIDE.get(design, "qwen3")
+            beside = (DESIGNS[other](layers, hidden, heads, inter, vocab) if other in DESIGNS
+                      else dict(_qwen3(layers, hidden, heads, inter, False), vocab_size=vocab))
+            for label, raw in ((design, DESIGNS[design](layers, hidden, heads, inter, vocab)), (other, beside)):
                 most = max(64 * (args.prompt_len + 600 + args.block_size), 8192 + 64)
                 runner, config = build_runner(raw, 64, most, args.block_size)
                 fill_cache_randomly(runner)
@@ -673,7 +709,8 @@ def run_design(args, measured, peak_kind) -> dict:
             "steps": main_point["steps_timed"], "warmup": args.warmup, "ms_per_step": main_point["ms"],
             "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic (random weights, random token ids)",
-            "config": {"model": f"{title} layers beside Qwen3 layers, {layers} layers each", "global_batch": 8,
+            "config": {"model": f"{title} layers beside {BESIDE.get(design, 'qwen3').capitalize()} layers, {layers} layers each",
+                       "global_batch": 8,
                        "seq_len": args.prompt_len, "parallelism": "single GPU", "vocab": vocab,
                        "l2": "weights and cache exceed L2 (126 MB) at every size"},
             "clocks": clocks.summary(), "peaks": {**measured, "kind": peak_kind}, "design": points}
@@ -865,8 +902,9 @@ def main() -> int:
     parser.add_argument("--layers", type=int, default=None, help="fewer layers than the shape has (named in config)")
     parser.add_argument("--block-size", type=int, default=16)
     parser.add_argument("--no-points", action="store_true", help="the main point only")
-    parser.add_argument("--design", default=None, choices=("bemuzen", "lobuzen", "nodopel"),
-                        help="instead of the default workload: layers of this design beside Qwen3 layers of equal sizes")
+    parser.add_argument("--design", default=None, choices=("bemuzen", "lobuzen", "nodopel", "mupuvik"),
+                        help="instead of the default workload: layers of this design beside Qwen3 layers of equal sizes "
+                             "(mupuvik: beside Bemuzen layers)")
     args = parser.parse_args()
 
     if args.gpus != 1:

@@ -158,6 +158,25 @@ def test_long_portions_beside_single_tokens(folders, references, dtype):
     compare(helpers.run_schedule(runner, sequences, steps), expected, dtype, f"{name}/long portions/{dtype}")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_long_portions_run_in_segments(folders, references, name, dtype, monkeypatch):
+    """Portions of 32 tokens and more are cut into segments of about 16 that run side by side, each from an empty
+    state, and are then corrected by the state they should have started from (decays per head in the scan, per
+    head and key channel in the gated linear attention): the same rows, for whole prompts, for portions that
+    start in the middle of a sequence, and beside single tokens."""
+    from vllm_from_scratch_b200.kernels import mixing
+    monkeypatch.setattr(mixing, "SCAN_SEGMENT", 16)
+    raw, page_size = CONFIGS[name]
+    sequences, expected = references[name, dtype]
+    for label, steps in (("whole", helpers.cut_whole(LENGTHS[name])),
+                         ("mixed", helpers.cut_mixed(LENGTHS[name], seed=5, live=3, sizes=(2, 33, 40, 64, 100)))):
+        pages = sum(sorted((-(-n // page_size) for n in LENGTHS[name].values()), reverse=True)[:3])
+        runner = make_runner(folders[name, dtype], dtype, page_size, pages, max_requests=3)
+        results = helpers.run_schedule(runner, sequences, steps)
+        compare(results, expected, dtype, f"{name}/segments/{label}/{dtype}")
+
+
 def test_long_decoding_keeps_the_state(folders, references):
     """A short prompt and 140 tokens decoded one by one through recurrences, the convolution and windows that
     have long passed the prompt."""
@@ -449,12 +468,17 @@ def test_attention_forms_far_keys_window_edges_and_page_borders(dtype, shape, fo
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("segments", [False, True])
 @pytest.mark.parametrize("shape", [(3, 40, 72), (2, 8, 16), (1, 132, 20), (6, 48, 32)])
-def test_gated_linear_attention_in_portions(dtype, shape):
+def test_gated_linear_attention_in_portions(dtype, shape, segments, monkeypatch):
     """Three requests advance through several steps in slots of their own, in portions of 1 to 21 tokens; the slot
     of the first is then used again by a new request.  The decays differ from channel to channel (logits from -4 to
-    6, so that some rows of the state are nearly kept and others nearly forgotten at every token)."""
+    6, so that some rows of the state are nearly kept and others nearly forgotten at every token).  ``segments``:
+    portions of 8 tokens and more run as segments of about 4 side by side."""
     from vllm_from_scratch_b200 import kernels
+    from vllm_from_scratch_b200.kernels import mixing
+    if segments:
+        monkeypatch.setattr(mixing, "SCAN_SEGMENT", 4)
     H, n, dv = shape
     g = torch.Generator().manual_seed(6)
     tau = 3.0
@@ -482,8 +506,9 @@ def test_gated_linear_attention_in_portions(dtype, shape):
     tol = 1e-4 if dtype == torch.float32 else 2e-2
 
     def run(pieces, z_pieces, starts, order, y):
+        longest = max(b - a for a, b in zip(starts, starts[1:])) if segments else None
         kernels.gated_linear_attention(dev(torch.cat(pieces)), offsets, dev(torch.cat(z_pieces)), 3, dev(gate_bias), tau,
-                                       n ** -0.5, i32(starts), i32(order), state, y, H, n, dv)
+                                       n ** -0.5, i32(starts), i32(order), state, y, H, n, dv, longest)
 
     for step in range(5):
         order = [3, 0, 1] if step % 2 else [1, 3, 0]

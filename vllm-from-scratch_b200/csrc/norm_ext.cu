@@ -248,6 +248,52 @@ __global__ void gated_group_norm_vec_kernel(const float* __restrict__ y, const T
     }
 }
 
+// Narrow groups (a head's values): a warp a token and group, eight of them a block; a lane holds up to two pieces
+// of four numbers.  FORM: 1 = silu of the gate ahead of the norm, 0 = sigmoid of the gate behind it, 2 = silu behind.
+template <typename T, int FORM>
+__global__ void gated_group_norm_warp_kernel(const float* __restrict__ y, const T* __restrict__ gate, int gate_stride,
+                                             const float* __restrict__ weight, T* __restrict__ out, int width,
+                                             int group_width, float eps, int out_stride, int tokens, int groups) {
+    overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
+    overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
+    const long long unit = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (unit >= (long long)tokens * groups) return;
+    const size_t token = (size_t)(unit / groups);
+    const int first = (int)(unit - (long long)token * groups) * group_width, lane = threadIdx.x & 31;
+    const float* y_row = y + token * width + first;
+    const T* g_row = gate + token * gate_stride + first;
+    float4 v[2], g[2];
+    float sum_sq = 0.0f;
+#pragma unroll
+    for (int step = 0; step < 2; ++step) {
+        const int i = (step * 32 + lane) * 4;
+        if (i < group_width) {
+            v[step] = load4(y_row + i);
+            const float4 z = load4(g_row + i);
+            if (FORM == 1) {
+                v[step].x *= z.x * sigmoid_f(z.x); v[step].y *= z.y * sigmoid_f(z.y);
+                v[step].z *= z.z * sigmoid_f(z.z); v[step].w *= z.w * sigmoid_f(z.w);
+            } else {
+                g[step] = make_float4(sigmoid_f(z.x), sigmoid_f(z.y), sigmoid_f(z.z), sigmoid_f(z.w));
+                if (FORM == 2) { g[step].x *= z.x; g[step].y *= z.y; g[step].z *= z.z; g[step].w *= z.w; }
+            }
+            sum_sq += dot4(v[step]);
+        }
+    }
+    const float inv = rsqrtf(warp_sum(sum_sq) / (float)group_width + eps);
+    T* o_row = out + token * out_stride + first;
+#pragma unroll
+    for (int step = 0; step < 2; ++step) {
+        const int i = (step * 32 + lane) * 4;
+        if (i < group_width) {
+            const float4 w = load4(weight + first + i), p = v[step];
+            float4 r = make_float4(p.x * inv * w.x, p.y * inv * w.y, p.z * inv * w.z, p.w * inv * w.w);
+            if (FORM != 1) { r.x *= g[step].x; r.y *= g[step].y; r.z *= g[step].z; r.w *= g[step].w; }
+            store4(o_row + i, r);
+        }
+    }
+}
+
 // Threads for a row of `width` elements taken four at a time, at most kRowSteps times a thread; 0 if
 // the row is too long for that.
 inline int vec_threads(int width) {
@@ -423,6 +469,17 @@ B200_EXPORT int b200_gated_group_norm_rows(const float* y, const void* gate, int
     const uintptr_t addresses = (uintptr_t)y | (uintptr_t)gate | (uintptr_t)weight | (uintptr_t)out;
     if (group_width % 4 == 0 && gate_stride % 4 == 0 && out_stride % 4 == 0 && (addresses & 15) == 0 && vec_threads(group_width) > 0 &&
         (dtype == 0 || dtype == 1)) {
+        if (group_width <= 256 && groups > 1) {
+            const long long units = (long long)tokens * groups;
+            const unsigned blocks = (unsigned)((units + 7) / 8);
+#define B200_WARP(T, FORM)                                                                                       \
+            launch_overlapped_if(tokens <= kOverlapMostRows, gated_group_norm_warp_kernel<T, FORM>, blocks, 256, 0, stream, y, \
+                                 (const T*)gate, gate_stride, weight, (T*)out, width, group_width, eps, out_stride, tokens, groups)
+            if (dtype == 0) { if (gate_first == 1) B200_WARP(float, 1); else if (gate_first == 2) B200_WARP(float, 2); else B200_WARP(float, 0); }
+            else { if (gate_first == 1) B200_WARP(__nv_bfloat16, 1); else if (gate_first == 2) B200_WARP(__nv_bfloat16, 2); else B200_WARP(__nv_bfloat16, 0); }
+#undef B200_WARP
+            return check_launch("gated_group_norm");
+        }
         const int threads = vec_threads(group_width);
 #define B200_VEC(T, FIRST)                                                                                      \
         launch_overlapped_if(tokens <= kOverlapMostRows, gated_group_norm_vec_kernel<T, FIRST>, grid, threads, 0, stream, y, (const T*)gate, gate_stride, weight, \

@@ -11,7 +11,9 @@
 //   head_gate          out[t, h, :] = x[t, h, :] * sigmoid(gate[t, h]) * factor
 //   scaled_sum         out = a * sa + b * sb
 //
-// Bias, statistics, weights, angles and the rotation are float32 in both run modes; one block per token.
+// Bias, statistics, weights, angles and the rotation are float32 in both run modes.  A token's head slots are
+// divided over blocks of a few warps, a warp a slot (every block of a token forms the sums over the whole
+// projection for itself where the norm is one over all heads: the row comes from L2 after the first).
 #include "common.cuh"
 
 namespace b200 {
@@ -68,7 +70,8 @@ __global__ void __launch_bounds__(256) qk_prepare_cache_kernel(const PrepareArgs
     }
     __syncthreads();
     const int page = store ? slot / p.page_size : 0, offset = store ? slot - page * p.page_size : 0;
-    for (int head_slot = warp; head_slot < nq + 2 * nkv; head_slot += warps) {
+    // A block's warps take the head slots blockIdx.y * warps .. (queries, then keys, then values), a slot each.
+    for (int head_slot = blockIdx.y * warps + warp; head_slot < nq + 2 * nkv; head_slot += gridDim.y * warps) {
         const bool is_q = head_slot < nq, is_k = !is_q && head_slot < nq + nkv;
         if (!is_q && !store) continue;
         if (!is_q && !is_k) {
@@ -176,12 +179,13 @@ B200_EXPORT int b200_qk_prepare_cache(
     PrepareArgs p = {qkv, bias, positions, slots, q_weight, k_weight, rotary_dim > 0 ? inv_freq : nullptr, q_out, k_pages,
                      v_pages, nq, nkv, d, dv, page_size, row_stride, norm_kind, rotary_dim, interleaved, eps};
     const int heads = nq + 2 * nkv;
-    const int threads = heads >= 8 ? 256 : heads >= 4 ? 128 : 64;
+    const int warps = 4;
+    const dim3 grid(num_tokens, min((heads + warps - 1) / warps, 65535));
     const size_t smem = sizeof(float) * (size_t)rotary_dim;
     if (dtype == 0)
-        launch_overlapped_if(num_tokens <= kOverlapMostRows, qk_prepare_cache_kernel<float>, num_tokens, threads, smem, stream, p);
+        launch_overlapped_if(num_tokens <= kOverlapMostRows, qk_prepare_cache_kernel<float>, grid, warps * 32, smem, stream, p);
     else if (dtype == 1)
-        launch_overlapped_if(num_tokens <= kOverlapMostRows, qk_prepare_cache_kernel<__nv_bfloat16>, num_tokens, threads, smem, stream, p);
+        launch_overlapped_if(num_tokens <= kOverlapMostRows, qk_prepare_cache_kernel<__nv_bfloat16>, grid, warps * 32, smem, stream, p);
     else
         return fail("qk_prepare_cache", "dtype must be 0 (float32) or 1 (bfloat16)");
     return check_launch("qk_prepare_cache");

@@ -352,6 +352,11 @@ struct GatedScanParams {
     const float* gate_bias;     // [H * N] or null
     float inv_tau, q_scale;
     int tokens;
+    // A long portion in segments, as in ScanParams; a segment's decays are a row of N numbers per head:
+    // seg_state [R * segs, H, N, dv], seg_decay [R * segs, H, N].
+    int mode, seg_len, segs;
+    float* seg_state;
+    float* seg_decay;
 };
 
 template <typename T, int NPT, int COLS>
@@ -366,18 +371,32 @@ __global__ void __launch_bounds__(kScanThreads) gated_linear_kernel(GatedScanPar
     float* a_s = q_s + kScanTile * kRows;                           // [tile][kRows]
     float* v_s = a_s + kScanTile * kRows;                           // [tile][COLS]
     float* part_s = v_s + kScanTile * kScanColumns;                 // [tile][parts][COLS]
-    const int request = blockIdx.x, head = blockIdx.y;
+    const int segs = p.mode == 0 ? 1 : p.segs;
+    const int request = blockIdx.x / segs, segment = blockIdx.x - request * segs, head = blockIdx.y;
+    const bool correct = p.mode == 2;
     const int tid = threadIdx.x, lane = tid % COLS, part = tid / COLS;
     const int column0 = blockIdx.z * kScanColumns, column = column0 + lane;
     const bool live = column < p.dv;
-    const int begin = p.query_start[request], end = p.query_start[request + 1];
+    int begin = p.query_start[request], end = p.query_start[request + 1];
+    if (p.mode != 0) {
+        begin += segment * p.seg_len;
+        end = min(end, begin + p.seg_len);
+        if (correct && segment == 0) return;        // the first segment started from the true state
+    }
     if (begin >= end) return;
     const int n = p.n;
     const int row0 = part * NPT;
     float* state = p.state + (((size_t)p.slots[request] * p.heads + head) * n) * p.dv + column;
-    float S[NPT];
+    float* left = p.mode == 0 ? state      // where the state goes at the end (mode 2: where it comes from)
+                              : p.seg_state + (((size_t)blockIdx.x * p.heads + head) * n) * p.dv + column;
+    const float* from = correct ? left : state;
+    const bool starts_empty = p.mode == 1 && segment > 0;
+    float S[NPT], decays[NPT];          // decays: the product of a row's decays over the tokens so far
 #pragma unroll
-    for (int i = 0; i < NPT; ++i) S[i] = (live && row0 + i < n) ? state[(size_t)(row0 + i) * p.dv] : 0.0f;
+    for (int i = 0; i < NPT; ++i) {
+        S[i] = (live && row0 + i < n && !starts_empty) ? from[(size_t)(row0 + i) * p.dv] : 0.0f;
+        decays[i] = 1.0f;
+    }
     const T* proj = (const T*)p.proj;
     const T* gate = (const T*)p.gate;
     const size_t y_stride = (size_t)p.heads * p.dv;
@@ -395,7 +414,7 @@ __global__ void __launch_bounds__(kScanThreads) gated_linear_kernel(GatedScanPar
             if (t < count && i < n) {
                 const size_t token = (size_t)(t0 + t);
                 const T* row = proj + token * p.stride;
-                kv = to_float(row[p.off_k + head * n + i]);
+                if (!correct) kv = to_float(row[p.off_k + head * n + i]);       // the second pass needs q and the decays alone
                 qv = to_float(row[p.off_q + head * n + i]);
                 zv = to_float(gate[token * p.gate_stride + p.off_gate + head * n + i]);
                 if (p.gate_bias) zv += p.gate_bias[head * n + i];
@@ -409,7 +428,7 @@ __global__ void __launch_bounds__(kScanThreads) gated_linear_kernel(GatedScanPar
             const int idx = tid + j * kScanThreads;
             const int t = idx / kScanColumns, c = idx - t * kScanColumns;
             float v = 0.0f;
-            if (t < count && column0 + c < p.dv)
+            if (t < count && column0 + c < p.dv && !correct)
                 v = to_float(proj[(size_t)(t0 + t) * p.stride + p.off_v + head * p.dv + column0 + c]);
             v_r[j] = v;
         }
@@ -440,6 +459,26 @@ __global__ void __launch_bounds__(kScanThreads) gated_linear_kernel(GatedScanPar
             const float* q_row = q_s + t * kRows + row0;
             const float* a_row = a_s + t * kRows + row0;
             float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            if (p.mode != 0) {
+#pragma unroll
+                for (int i = 0; i < NPT; i += 4) {
+                    const float4 a4 = *reinterpret_cast<const float4*>(a_row + i);
+                    decays[i] *= a4.x; decays[i + 1] *= a4.y; decays[i + 2] *= a4.z; decays[i + 3] *= a4.w;
+                }
+            }
+            if (correct) {
+                // what the state this segment should have started from adds: (a_first .. a_t) * C, row by row
+#pragma unroll
+                for (int i = 0; i < NPT; i += 4) {
+                    const float4 q4 = *reinterpret_cast<const float4*>(q_row + i);
+                    acc[0] = fmaf(S[i] * decays[i], q4.x, acc[0]);
+                    acc[1] = fmaf(S[i + 1] * decays[i + 1], q4.y, acc[1]);
+                    acc[2] = fmaf(S[i + 2] * decays[i + 2], q4.z, acc[2]);
+                    acc[3] = fmaf(S[i + 3] * decays[i + 3], q4.w, acc[3]);
+                }
+                part_s[(t * kScanParts + part) * kScanColumns + lane] = (acc[0] + acc[1]) + (acc[2] + acc[3]);
+                continue;
+            }
 #pragma unroll
             for (int i = 0; i < NPT; i += 4) {
                 const float4 k4 = *reinterpret_cast<const float4*>(k_row + i);
@@ -463,13 +502,50 @@ __global__ void __launch_bounds__(kScanThreads) gated_linear_kernel(GatedScanPar
             float total = 0.0f;
 #pragma unroll
             for (int w = 0; w < kScanParts; ++w) total += part_s[(t * kScanParts + w) * kScanColumns + c];
-            p.y[(size_t)(t0 + t) * y_stride + head * p.dv + column0 + c] = total;
+            float* y = p.y + (size_t)(t0 + t) * y_stride + head * p.dv + column0 + c;
+            if (correct) *y += total;
+            else *y = total;
         }
     }
+    if (correct) return;
     if (live) {
 #pragma unroll
         for (int i = 0; i < NPT; ++i)
-            if (row0 + i < n) state[(size_t)(row0 + i) * p.dv] = S[i];
+            if (row0 + i < n) left[(size_t)(row0 + i) * p.dv] = S[i];
+    }
+    if (p.mode == 1 && lane == 0 && blockIdx.z == 0) {
+#pragma unroll
+        for (int i = 0; i < NPT; ++i)
+            if (row0 + i < n) p.seg_decay[((size_t)blockIdx.x * p.heads + head) * n + row0 + i] = decays[i];
+    }
+}
+
+// As carry_states_kernel, with a decay per row of a head's state: seg_decay [R * segs, H, N].
+__global__ void carry_states_rows_kernel(float* __restrict__ seg_state, const float* __restrict__ seg_decay,
+                                         float* __restrict__ state, const int* __restrict__ query_start,
+                                         const int* __restrict__ slots, int heads, int n, int dv, int seg_len, int segs) {
+    overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
+    overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
+    const int request = blockIdx.x, head = blockIdx.y;
+    const int length = query_start[request + 1] - query_start[request];
+    if (length <= 0) return;
+    const int used = (length + seg_len - 1) / seg_len;
+    const int elements = n * dv;
+    for (int e = blockIdx.z * blockDim.x + threadIdx.x; e < elements; e += gridDim.z * blockDim.x) {
+        const int row = e / dv;
+        float carried = 0.0f;
+        for (int s = 0; s < used; ++s) {
+            const size_t at = ((size_t)request * segs + s) * heads + head;
+            float* cell = seg_state + at * elements + e;
+            const float ended = *cell;
+            if (s > 0) {
+                *cell = carried;                                    // what the second pass starts from
+                carried = fmaf(seg_decay[at * n + row], carried, ended);
+            } else {
+                carried = ended;
+            }
+        }
+        state[((size_t)slots[request] * heads + head) * elements + e] = carried;
     }
 }
 
@@ -482,9 +558,18 @@ int launch_gated_rows(const GatedScanParams& p, int requests, cudaStream_t strea
         cudaError_t status = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (status != cudaSuccess) return fail("gated_linear_attention", cudaGetErrorString(status));
     }
-    dim3 grid(requests, p.heads, (p.dv + COLS - 1) / COLS);
+    dim3 grid(requests * (p.mode == 0 ? 1 : p.segs), p.heads, (p.dv + COLS - 1) / COLS);
     launch_overlapped_if(p.tokens <= kOverlapMostRows, kernel, grid, kScanThreads, smem, stream, p);
-    return check_launch("gated_linear_attention");
+    if (int status = check_launch("gated_linear_attention")) return status;
+    if (p.mode != 1) return 0;
+    const int elements = p.n * p.dv;
+    launch_overlapped_if(false, carry_states_rows_kernel, dim3(requests, p.heads, min((elements + 255) / 256, 64)), 256, 0,
+        stream, p.seg_state, p.seg_decay, p.state, p.query_start, p.slots, p.heads, p.n, p.dv, p.seg_len, p.segs);
+    if (int status = check_launch("carry_states")) return status;
+    GatedScanParams again = p;
+    again.mode = 2;
+    launch_overlapped_if(false, kernel, grid, kScanThreads, smem, stream, again);
+    return check_launch("gated_linear_attention (second pass)");
 }
 
 template <typename T>
@@ -494,7 +579,8 @@ int launch_gated(const GatedScanParams& p, int requests, cudaStream_t stream) {
     if (p.n > 256) return fail("gated_linear_attention", "a state of more than 256 rows per head is not built");
     const long long sms = sm_count() > 0 ? sm_count() : 1;
     int cols = 32;
-    while (cols > 8 && (long long)requests * p.heads * ((p.dv + cols - 1) / cols) < sms && p.n > 32 * (32 / cols)) cols /= 2;
+    const long long rows_of_blocks = (long long)requests * (p.mode == 0 ? 1 : p.segs);
+    while (cols > 8 && rows_of_blocks * p.heads * ((p.dv + cols - 1) / cols) < sms && p.n > 32 * (32 / cols)) cols /= 2;
 #define B200_ROWS(NPT, COLS) return launch_gated_rows<T, NPT, COLS>(p, requests, stream)
     if (cols == 32) {
         if (p.n <= 32) B200_ROWS(4, 32);
@@ -662,12 +748,14 @@ B200_EXPORT int b200_selective_scan(const float* xbc, int xbc_width, const void*
 // off_v; q and k are heads x n, v heads x dv; no activation, q times q_scale).  The decays' logits are the
 // columns off_gate .. off_gate + heads * n of `gate` [T, gate_stride] (same dtype as proj), plus gate_bias
 // (float32 [heads * n] or null); decay = sigmoid(logit) ^ inv_tau.  y: float32 [T, heads * dv].  state: float32
-// [slots + 1, heads, n, dv].
+// [slots + 1, heads, n, dv].  segs > 1: long portions run in segments of seg_len tokens side by side; seg_state holds
+// [requests * segs, heads, n, dv] floats and seg_decay [requests * segs, heads, n].
 B200_EXPORT int b200_gated_linear_attention(const void* proj, int stride, int off_q, int off_k, int off_v,
                                             const void* gate, int gate_stride, int off_gate, const float* gate_bias,
                                             float inv_tau, float q_scale, const int* query_start, const int* slots,
                                             float* state, float* y, int tokens, int requests, int heads, int n, int dv,
-                                            int dtype, cudaStream_t stream) {
+                                            int seg_len, int segs, float* seg_state, float* seg_decay, int dtype,
+                                            cudaStream_t stream) {
     using namespace b200;
     if (requests == 0) return 0;
     GatedScanParams p = {};
@@ -676,6 +764,12 @@ B200_EXPORT int b200_gated_linear_attention(const void* proj, int stride, int of
     p.proj = proj; p.stride = stride; p.off_q = off_q; p.off_k = off_k; p.off_v = off_v;
     p.gate = gate; p.gate_stride = gate_stride; p.off_gate = off_gate; p.gate_bias = gate_bias;
     p.inv_tau = inv_tau; p.q_scale = q_scale;
+    p.mode = 0; p.seg_len = 0; p.segs = 1; p.seg_state = nullptr; p.seg_decay = nullptr;
+    if (segs > 1) {
+        if (seg_len <= 0 || seg_state == nullptr || seg_decay == nullptr)
+            return fail("gated_linear_attention", "segments need a length and scratch for their states and decays");
+        p.mode = 1; p.seg_len = seg_len; p.segs = segs; p.seg_state = seg_state; p.seg_decay = seg_decay;
+    }
     if (dtype == 0) return launch_gated<float>(p, requests, stream);
     if (dtype == 1) return launch_gated<__nv_bfloat16>(p, requests, stream);
     return fail("gated_linear_attention", "dtype must be 0 (float32) or 1 (bfloat16)");

@@ -368,15 +368,21 @@ def decayed_linear_attention(proj: torch.Tensor, offsets: tuple[int, int, int], 
 def gated_linear_attention(proj: torch.Tensor, offsets: tuple[int, int, int], gate: torch.Tensor, gate_offset: int,
                            gate_bias: torch.Tensor | None, tau: float, q_scale: float, query_start: torch.Tensor,
                            slots: torch.Tensor, state: torch.Tensor, y: torch.Tensor, heads: int, key_dim: int,
-                           value_dim: int) -> None:
+                           value_dim: int, max_query_len: int | None = None) -> None:
     """Per request and head, token after token: ``S <- diag(a) S + k v^T``, ``y = S^T (q * q_scale)`` with q, k
     (``heads x key_dim``) and v (``heads x value_dim``) the columns of ``proj`` that start at ``offsets = (q, k,
     v)``, as projected, and a decay per head and key channel ``a = sigmoid(z) ** (1 / tau)``, ``z`` = the columns
     ``gate_offset .. gate_offset + heads * key_dim`` of ``gate`` plus ``gate_bias`` (float32), formed in float32.
     ``state``: float32 ``[slots + 1, heads, key_dim, value_dim]``, read at the request's slot and left advanced;
-    ``y``: float32 ``[T, heads * value_dim]``."""
+    ``y``: float32 ``[T, heads * value_dim]``.  With ``max_query_len`` (the longest portion of the step) long
+    portions run in segments side by side."""
     tokens, stride = proj.shape
     requests = slots.shape[0]
+    seg_len, segs, seg_state, _ = _segments(max_query_len, requests, heads, key_dim, value_dim, proj.device)
+    seg_decay = None
+    if segs > 1:
+        seg_decay = torch.empty((requests * segs, heads, key_dim), dtype=torch.float32, device=proj.device)
+        count_launch(2)
     if tau <= 0:
         from . import KernelError
         raise KernelError(f"gated linear attention: tau={tau} must be positive")
@@ -389,7 +395,9 @@ def gated_linear_attention(proj: torch.Tensor, offsets: tuple[int, int, int], ga
          _P(_check("state slots", slots, torch.int32, (requests,))),
          _P(_check("state", state, torch.float32, (None, heads, key_dim, value_dim))),
          _P(_check("recurrence output", y, torch.float32, (tokens, heads * value_dim))),
-         _I(tokens), _I(requests), _I(heads), _I(key_dim), _I(value_dim), _I(_code(proj.dtype)), _stream())
+         _I(tokens), _I(requests), _I(heads), _I(key_dim), _I(value_dim), _I(seg_len), _I(segs),
+         _P(seg_state.data_ptr() if segs > 1 else 0), _P(seg_decay.data_ptr() if segs > 1 else 0),
+         _I(_code(proj.dtype)), _stream())
 
 
 def selective_scan(xbc: torch.Tensor, proj: torch.Tensor, dt_offset: int, dt_bias: torch.Tensor,

@@ -167,7 +167,8 @@ class GatedLinearAttention(Mixer):
         y = torch.empty((tokens, self.inner), dtype=torch.float32, device=x.device)
         kernels.gated_linear_attention(proj, (self.inner, self.inner + keys, self.inner + 2 * keys), logits, 0,
                                        self.up_bias, self.tau, self.head_dim ** -0.5, ctx.query_start,
-                                       ctx.state_slots, state, y, self.num_heads, self.head_dim, self.value_dim)
+                                       ctx.state_slots, state, y, self.num_heads, self.head_dim, self.value_dim,
+                                       ctx.max_query_len)
         gated = out if out is not None else torch.empty((tokens, self.inner), dtype=x.dtype, device=x.device)
         factor = factor * self.out_scale
         if factor not in self._scaled_norms:        # the factor rides on the norm's weights (float32, formed once)
