@@ -424,6 +424,16 @@ def test_attention_forms_far_keys_window_edges_and_page_borders(dtype, shape, fo
     kernels.qk_prepare_cache(dev(qkv, dtype), None if bias is None else dev(bias), i32(positions), i32(slots), dev(qw), dev(kw),
                              spec["norm"], eps, None if inv_freq is None else dev(inv_freq, torch.float32), rot_dims, True,
                              q_out, k_d, v_d, H, G, d, dv, page)
+    # Rows a multiple of four numbers long take the kernel's form of four numbers a lane: the same queries and pages.
+    wider = torch.zeros(tokens, (H + G) * d + G * dv + 8, dtype=torch.float64)
+    wider[:, :qkv.shape[1]] = qkv
+    k_d2, v_d2, q_out2 = dev(k_pool), dev(v_pool), torch.empty_like(q_out)
+    kernels.qk_prepare_cache(dev(wider, dtype), None if bias is None else dev(bias), i32(positions), i32(slots), dev(qw), dev(kw),
+                             spec["norm"], eps, None if inv_freq is None else dev(inv_freq, torch.float32), rot_dims, True,
+                             q_out2, k_d2, v_d2, H, G, d, dv, page)
+    close = dict(atol=1e-5, rtol=1e-5) if dtype == torch.float32 else dict(atol=2e-2, rtol=2e-2)
+    for one, other in ((q_out, q_out2), (k_d, k_d2), (v_d, v_d2)):
+        assert torch.allclose(one.float(), other.float(), **close)
     sinks = torch.zeros(H, device="cuda") if sink else None
     tol = 2e-5 if dtype == torch.float32 else 4e-2
 

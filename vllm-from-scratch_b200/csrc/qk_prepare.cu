@@ -129,6 +129,117 @@ __global__ void __launch_bounds__(256) qk_prepare_cache_kernel(const PrepareArgs
     }
 }
 
+__device__ __forceinline__ float4 four(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 four(const __nv_bfloat16* p) {
+    const uint2 raw = *reinterpret_cast<const uint2*>(p);
+    const float2 lo = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 hi = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    return make_float4(lo.x, lo.y, hi.x, hi.y);
+}
+__device__ __forceinline__ void put_four(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void put_four(__nv_bfloat16* p, float4 v) {
+    const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw;
+    raw.x = *reinterpret_cast<const unsigned*>(&lo);
+    raw.y = *reinterpret_cast<const unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// The same for sizes that are multiples of four and rows that begin at 16 bytes (8 in bfloat16), with the pairs of
+// a rotation neighbours (or none): a lane holds four consecutive numbers of a head (up to four such pieces for
+// heads of up to 512), so a head is read once, both numbers of a pair lie in one lane, and every access is 8 or 16
+// bytes wide.  The same arithmetic in the same order per number as in the kernel above but for the sums of
+// squares, which are added four numbers a lane.
+template <typename T>
+__global__ void __launch_bounds__(256) qk_prepare_cache_vec_kernel(const PrepareArgs p) {
+    overlap_trigger();      // the kernel behind may be scheduled while this one runs ...
+    overlap_wait();         // ... and this one touches nothing before the kernel ahead is done
+    __shared__ float scratch[33];
+    __shared__ float whole_s[2];
+    extern __shared__ float turn_s[];           // [rotary_dim / 2] cosines, then as many sines
+    const int token = blockIdx.x;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int nq = p.nq, nkv = p.nkv, d = p.d, dv = p.dv;
+    const T* row = (const T*)p.qkv + (size_t)token * p.row_stride;
+    const int slot = p.slots[token];
+    const bool store = p.k_pages != nullptr && nkv > 0 && slot >= 0;
+    const int half = p.rotary_dim / 2;
+    if (p.inv_freq != nullptr && half > 0) {
+        const float position = (float)p.positions[token];
+        for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf(position * p.inv_freq[i], &turn_s[half + i], &turn_s[i]);
+    }
+    if (p.norm_kind == kNormWhole) {
+        for (int which = 0; which < 2; ++which) {
+            const int first = which == 0 ? 0 : nq * d, count = which == 0 ? nq * d : nkv * d;
+            float sum = 0.0f;
+            for (int i = threadIdx.x * 4; i < count; i += blockDim.x * 4) {
+                float4 v = four(row + first + i);
+                if (p.bias) { const float4 b = four(p.bias + first + i); v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w; }
+                sum += (v.x * v.x + v.y * v.y) + (v.z * v.z + v.w * v.w);
+            }
+            sum = block_sum(sum, scratch);
+            if (threadIdx.x == 0) whole_s[which] = count > 0 ? rsqrtf(sum / (float)count + p.eps) : 0.0f;
+        }
+    }
+    __syncthreads();
+    const int page = store ? slot / p.page_size : 0, offset = store ? slot - page * p.page_size : 0;
+    const int rotated = p.inv_freq != nullptr ? p.rotary_dim : 0;       // numbers of a head that are turned
+    for (int head_slot = blockIdx.y * warps + warp; head_slot < nq + 2 * nkv; head_slot += gridDim.y * warps) {
+        const bool is_q = head_slot < nq, is_k = !is_q && head_slot < nq + nkv;
+        if (!is_q && !store) continue;
+        if (!is_q && !is_k) {
+            const int kv_head = head_slot - nq - nkv;
+            const int first = (nq + nkv) * d + kv_head * dv;
+            T* dst = (T*)p.v_pages + (((size_t)page * nkv + kv_head) * p.page_size + offset) * dv;
+            for (int j = lane * 4; j < dv; j += 128) {
+                float4 v = four(row + first + j);
+                if (p.bias) { const float4 b = four(p.bias + first + j); v.x += b.x; v.y += b.y; v.z += b.z; v.w += b.w; }
+                put_four(dst + j, v);
+            }
+            continue;
+        }
+        const int first = head_slot * d;
+        const int head = is_q ? head_slot : head_slot - nq;
+        const float* weight = is_q ? p.q_weight : p.k_weight;
+        if (weight != nullptr && p.norm_kind == kNormWhole) weight += (size_t)head * d;
+        float4 v[4];
+        float sum = 0.0f;
+#pragma unroll
+        for (int step = 0; step < 4; ++step) {
+            const int j = (step * 32 + lane) * 4;
+            if (j < d) {
+                v[step] = four(row + first + j);
+                if (p.bias) {
+                    const float4 b = four(p.bias + first + j);
+                    v[step].x += b.x; v[step].y += b.y; v[step].z += b.z; v[step].w += b.w;
+                }
+                sum += (v[step].x * v[step].x + v[step].y * v[step].y) + (v[step].z * v[step].z + v[step].w * v[step].w);
+            }
+        }
+        float factor = 1.0f;
+        if (p.norm_kind == kNormWhole) factor = whole_s[is_q ? 0 : 1];
+        else if (p.norm_kind == kNormHead) factor = rsqrtf(warp_sum(sum) / (float)d + p.eps);
+        T* dst = is_q ? (T*)p.q_out + ((size_t)token * nq + head) * d
+                      : (T*)p.k_pages + (((size_t)page * nkv + head) * p.page_size + offset) * d;
+#pragma unroll
+        for (int step = 0; step < 4; ++step) {
+            const int j = (step * 32 + lane) * 4;
+            if (j >= d) continue;
+            float4 r = make_float4(v[step].x * factor, v[step].y * factor, v[step].z * factor, v[step].w * factor);
+            if (weight != nullptr) { const float4 w = four(weight + j); r.x *= w.x; r.y *= w.y; r.z *= w.z; r.w *= w.w; }
+            if (j < rotated) {
+                const int pair = j >> 1;
+                rotate_pair(r.x, r.y, turn_s[pair], turn_s[half + pair], r.x, r.y);
+            }
+            if (j + 2 < rotated) {
+                const int pair = (j >> 1) + 1;
+                rotate_pair(r.z, r.w, turn_s[pair], turn_s[half + pair], r.z, r.w);
+            }
+            put_four(dst + j, r);
+        }
+    }
+}
+
 // out[t, h, :] = x[t, h, :] * sigmoid(gate[t * gate_stride + h]) * factor; one block per token.
 template <typename T>
 __global__ void head_gate_kernel(const T* __restrict__ x, const T* __restrict__ gate, int gate_stride,
@@ -178,11 +289,23 @@ B200_EXPORT int b200_qk_prepare_cache(
     if (inv_freq == nullptr) rotary_dim = 0;
     PrepareArgs p = {qkv, bias, positions, slots, q_weight, k_weight, rotary_dim > 0 ? inv_freq : nullptr, q_out, k_pages,
                      v_pages, nq, nkv, d, dv, page_size, row_stride, norm_kind, rotary_dim, interleaved, eps};
+    // A token's head slots go to as many blocks of eight warps as it takes to give the GPU two blocks an SM.
     const int heads = nq + 2 * nkv;
-    const int warps = 4;
-    const dim3 grid(num_tokens, min((heads + warps - 1) / warps, 65535));
+    const int warps = heads >= 8 ? 8 : heads >= 4 ? 4 : 2;
+    const int sms = sm_count() > 0 ? sm_count() : 1;
+    const int chunks = max(1, min((heads + warps - 1) / warps, (2 * sms + num_tokens - 1) / num_tokens));
+    const dim3 grid(num_tokens, chunks);
     const size_t smem = sizeof(float) * (size_t)rotary_dim;
-    if (dtype == 0)
+    const size_t element = dtype == 0 ? 4 : 2;
+    const uintptr_t addresses = (uintptr_t)qkv | (uintptr_t)bias | (uintptr_t)q_weight | (uintptr_t)k_weight |
+                                (uintptr_t)q_out | (uintptr_t)k_pages | (uintptr_t)v_pages;
+    const bool vec = d % 4 == 0 && dv % 4 == 0 && d <= 512 && row_stride % 4 == 0 && (addresses & 15) == 0 &&
+                     (rotary_dim == 0 || interleaved) && (dtype == 0 || dtype == 1) && element > 0;
+    if (vec && dtype == 0)
+        launch_overlapped_if(num_tokens <= kOverlapMostRows, qk_prepare_cache_vec_kernel<float>, grid, warps * 32, smem, stream, p);
+    else if (vec)
+        launch_overlapped_if(num_tokens <= kOverlapMostRows, qk_prepare_cache_vec_kernel<__nv_bfloat16>, grid, warps * 32, smem, stream, p);
+    else if (dtype == 0)
         launch_overlapped_if(num_tokens <= kOverlapMostRows, qk_prepare_cache_kernel<float>, grid, warps * 32, smem, stream, p);
     else if (dtype == 1)
         launch_overlapped_if(num_tokens <= kOverlapMostRows, qk_prepare_cache_kernel<__nv_bfloat16>, grid, warps * 32, smem, stream, p);
